@@ -1,0 +1,61 @@
+"""Tiny configurations and helpers shared by the tests.
+
+Two configurations of the architecture that differ in every size and option:
+layers 2/3, hidden 64/96, heads 4/3, key/value heads 2/1, head size 16/32,
+intermediate 176/256, vocabulary 256/384, theta 1e4/1e6, window 16/none, eps
+1e-5/1e-6; a third has a head size that is not hidden/heads and a vocabulary that
+is no multiple of 8."""
+from __future__ import annotations
+
+import os
+import tempfile
+
+import numpy as np
+import torch
+
+TINY_A = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "intermediate_size": 176, "vocab_size": 256,
+    "rope_theta": 10000.0, "sliding_window": 16, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+TINY_B = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "intermediate_size": 256, "vocab_size": 384,
+    "rope_theta": 1000000.0, "sliding_window": None, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+TINY_C = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 80, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 48, "intermediate_size": 200, "vocab_size": 331,
+    "rope_theta": 50000.0, "sliding_window": 70, "rms_norm_eps": 3e-6,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def make_model_dir(cfg: dict, seed: int, dtype=torch.bfloat16, where: str | None = None) -> str:
+    """Writes a random model folder into a temporary place and returns it."""
+    from torchless_rs_b200 import write_random_model
+    from torchless_rs_b200.config import config_from_dict
+    d = where or tempfile.mkdtemp(prefix="tl_model_")
+    write_random_model(config_from_dict(cfg), d, seed, dtype)
+    return d
+
+
+def read_weights_numpy(model_dir: str) -> dict:
+    """The folder's tensors as float32 numpy arrays, read with the `safetensors`
+    package (not with the package under test)."""
+    from safetensors import safe_open
+    out = {}
+    with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            out[k] = f.get_tensor(k).to(torch.float32).numpy()
+    return out
+
+
+def random_tokens(rng: np.random.Generator, n: int, vocab: int) -> list:
+    return [int(t) for t in rng.integers(0, vocab, size=n)]

@@ -1,0 +1,111 @@
+"""The Python entry point: load a model folder, generate, or drive steps by hand.
+
+    import torchless_rs_b200 as tl
+    m = tl.load("model_dir", dtype="bfloat16", max_tokens=8192)
+    out = m.generate([[1, 5, 9], [1, 7]], max_tokens=16, temperature=0.0)
+
+(The reference's library surface, for comparison: docs/library.md:21-139,
+src/lib.rs:54-91: load parameters, build the model, create a state, call forward
+and a sampler.)"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Union
+
+import torch
+
+from .config import load_config
+from .engine.engine import Engine
+from .engine.generate import GenerationResult, generate as _generate
+from .engine.model import expected_tensors
+from .parts.runtime import Runtime
+from .sampling.params import SamplingParams
+from .weights.loader import load_checked
+from .weights.random_init import random_tensors
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, "f32": torch.float32}
+
+
+def parse_dtype(dtype: Union[str, torch.dtype]) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype in (torch.bfloat16, torch.float32):
+            return dtype
+    elif str(dtype).lower() in _DTYPES:
+        return _DTYPES[str(dtype).lower()]
+    raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
+
+
+class Model:
+    """A loaded model with its cache.  `config` is the typed configuration;
+    `engine` gives `step`, `start_sequences`, `end_sequences`."""
+
+    def __init__(self, config, engine: Engine):
+        from .sampling.sampler import Sampler
+        self.config = config
+        self.engine = engine
+        self.sampler = Sampler(engine.rt.device)
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 16,
+                 temperature: float = 0.0, top_k: Optional[int] = None,
+                 top_p: Optional[float] = None, stop_ids: Optional[Sequence[int]] = None,
+                 seed: int = 0, on_token: Optional[Callable[[int, int], None]] = None,
+                 max_batch: Optional[int] = None) -> List[GenerationResult]:
+        """Token ids in (host lists), token ids out.  `stop_ids` defaults to the
+        configuration's end tokens; pass () for none."""
+        params = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p)
+        if stop_ids is None:
+            stop_ids = self.engine.spec.stop_token_ids
+        return _generate(self.engine, self.sampler.select, prompts, max_tokens, params, stop_ids,
+                         seed, on_token, max_batch=max_batch)
+
+    def step(self, slots, tokens, want="last"):
+        return self.engine.step(slots, tokens, want)
+
+    def start_sequences(self, count: int):
+        return self.engine.start_sequences(count)
+
+    def end_sequences(self, slots) -> None:
+        self.engine.end_sequences(slots)
+
+
+def _default_max_tokens(config) -> int:
+    return int(getattr(config, "max_position_embeddings", 4096))
+
+
+def load(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
+         max_tokens: Optional[int] = None, max_batch: Optional[int] = None,
+         max_seq_len: Optional[int] = None, device: str = "cuda:0") -> Model:
+    """Loads `config.json` and the safetensors weights of `model_dir`.  The model
+    class is chosen by config.json through the architecture registry."""
+    config = load_config(model_dir)
+    spec = config.model_spec()
+    rt = Runtime(device, parse_dtype(dtype))
+    weights, source = load_checked(model_dir, expected_tensors(spec))
+    try:
+        engine = Engine(spec, weights, rt, max_tokens or _default_max_tokens(config),
+                        max_batch, max_seq_len)
+    finally:
+        del weights
+        source.close()
+    return Model(config, engine)
+
+
+def from_random(config, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16",
+                max_tokens: Optional[int] = None, max_batch: Optional[int] = None,
+                max_seq_len: Optional[int] = None, device: str = "cuda:0") -> Model:
+    """A model with random weights drawn on the device, without a model folder
+    (for measurements at sizes whose folder would be tens of gigabytes)."""
+    spec = config.model_spec()
+    adt = parse_dtype(dtype)
+    rt = Runtime(device, adt)
+
+    class _Lazy(dict):
+        def __missing__(self, name):
+            return None
+    exp = expected_tensors(spec)
+    weights = {n: t for n, t in random_tensors(exp, seed, adt, rt.device)}
+    engine = Engine(spec, weights, rt, max_tokens or _default_max_tokens(config), max_batch,
+                    max_seq_len)
+    del weights
+    torch.cuda.empty_cache()
+    return Model(config, engine)

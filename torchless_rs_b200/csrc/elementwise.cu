@@ -1,0 +1,165 @@
+// Memory-bound parts of the step: embedding gather, RMSNorm, rotation + cache
+// write, SiLU-gate.  The residual stream is always 32-bit; `act_t` is the type
+// of what feeds the matrix products and of the cache.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: x[t, :] = table[tokens[t], :], no scaling
+// (reference: src/model/modules/embedding.rs:15-21).
+// ---------------------------------------------------------------------------
+__global__ void embed_kernel(const int* __restrict__ tokens, const act_t* __restrict__ table,
+                             float* __restrict__ x, int H, int vocab) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // the host has checked the range already
+  const act_t* src = table + (size_t)tok * H;
+  float* dst = x + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32(src[i]);
+}
+
+extern "C" int TL_NAME(tl_embed)(const int* tokens, const void* table, float* x, int T, int H,
+                                 int vocab, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  embed_kernel<<<T, 256, 0, stream>>>(tokens, (const act_t*)table, x, H, vocab);
+  return TL_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm: y = (x / sqrt(mean(x^2) + eps)) * w, all in 32-bit, output rounded to
+// act_t (reference: src/kernels/mod.rs:558-568).  `rows` (optional) picks the
+// input rows, so the final norm runs on the wanted rows only.
+// ---------------------------------------------------------------------------
+template <typename W>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                               const W* __restrict__ w, act_t* __restrict__ y, int H, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+  act_t* yr = y + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    yr[i] = from_f32<act_t>((xr[i] / rms) * to_f32(w[i]));
+}
+
+extern "C" int TL_NAME(tl_rmsnorm)(const float* x, const int* rows, const void* w, int w_is_f32,
+                                   void* y, int n_rows, int H, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const int threads = H >= 2048 ? 512 : 256;
+  if (w_is_f32)
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, (const float*)w, (act_t*)y, H, eps);
+  else
+    rmsnorm_kernel<__nv_bfloat16>
+        <<<n_rows, threads, 0, stream>>>(x, rows, (const __nv_bfloat16*)w, (act_t*)y, H, eps);
+  return TL_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Rotation of q and k at each token's own position and the write of k and v into
+// the token's cache page (reference: rotation src/kernels/mod.rs:572-608, cache
+// write src/model/kv_cache.rs:87-104; v is not rotated).
+//   qkv      [T, ld] 32-bit: nh*hd columns of q, then nkv*hd of k, then nkv*hd of v
+//   q_out    [T, nh*hd]
+//   k_pages, v_pages  [n_pages, nkv, TL_PAGE, hd]; null when the layer keeps no cache
+//   inv_freq [hd/2] 32-bit, null for no rotation
+//   style 0: dimension i pairs with i + hd/2;  style 1: 2i pairs with 2i+1
+// The angle pos * inv_freq and its sine and cosine are computed in 32-bit.
+// ---------------------------------------------------------------------------
+__global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
+                                        act_t* __restrict__ q_out, act_t* __restrict__ k_pages,
+                                        act_t* __restrict__ v_pages,
+                                        const int* __restrict__ token_pos,
+                                        const int* __restrict__ token_seq,
+                                        const int* __restrict__ seq_slot,
+                                        const int* __restrict__ page_table, int table_stride,
+                                        const float* __restrict__ inv_freq, int style, int nh,
+                                        int nkv, int hd) {
+  const int t = blockIdx.x;
+  const int pos = token_pos[t];
+  const int half = hd >> 1;
+  const float* row = qkv + (size_t)t * ld;
+  const bool has_kv = k_pages != nullptr;
+  size_t page_base = 0;
+  bool page_ok = false;
+  if (has_kv) {
+    const int slot = seq_slot[token_seq[t]];
+    const int page = page_table[(size_t)slot * table_stride + pos / TL_PAGE];
+    page_ok = page >= 0;
+    page_base = (size_t)(page_ok ? page : 0) * nkv * TL_PAGE * hd + (size_t)(pos % TL_PAGE) * hd;
+  }
+  const int n_rot_heads = nh + (has_kv ? nkv : 0);
+  const float fpos = (float)pos;
+  for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    const int d0 = style == 0 ? i : 2 * i;
+    const int d1 = style == 0 ? i + half : 2 * i + 1;
+    const float a = row[h * hd + d0], b = row[h * hd + d1];
+    float ra = a, rb = b;
+    if (inv_freq) {
+      float s, c;
+      sincosf(fpos * inv_freq[i], &s, &c);
+      ra = a * c - b * s;
+      rb = a * s + b * c;
+    }
+    if (h < nh) {
+      act_t* dst = q_out + (size_t)t * nh * hd + h * hd;
+      dst[d0] = from_f32<act_t>(ra);
+      dst[d1] = from_f32<act_t>(rb);
+    } else if (page_ok) {
+      act_t* dst = k_pages + page_base + (size_t)(h - nh) * TL_PAGE * hd;
+      dst[d0] = from_f32<act_t>(ra);
+      dst[d1] = from_f32<act_t>(rb);
+    }
+  }
+  if (has_kv && page_ok) {
+    const float* vrow = row + (size_t)(nh + nkv) * hd;
+    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+      const int h = idx / hd, d = idx - h * hd;
+      v_pages[page_base + (size_t)h * TL_PAGE * hd + d] = from_f32<act_t>(vrow[idx]);
+    }
+  }
+}
+
+extern "C" int TL_NAME(tl_rope_cache_write)(const float* qkv, int ld, void* q_out, void* k_pages,
+                                            void* v_pages, const int* token_pos,
+                                            const int* token_seq, const int* seq_slot,
+                                            const int* page_table, int table_stride,
+                                            const float* inv_freq, int style, int T, int nh,
+                                            int nkv, int hd, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd & 1) return TL_ERR_BAD_ARG;
+  rope_cache_write_kernel<<<T, 128, 0, stream>>>(qkv, ld, (act_t*)q_out, (act_t*)k_pages,
+                                                 (act_t*)v_pages, token_pos, token_seq, seq_slot,
+                                                 page_table, table_stride, inv_freq, style, nh,
+                                                 nkv, hd);
+  return TL_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// SiLU-gate on an unfused gate/up product: out[t, j] = silu(gu[t, j]) * gu[t, I + j]
+// with silu(z) = z / (1 + exp(-z)) (reference: src/kernels/mod.rs:546-548,
+// src/model/modules/mlp.rs:34-40).
+// ---------------------------------------------------------------------------
+__global__ void silu_mul_kernel(const float* __restrict__ gu, act_t* __restrict__ out, int I,
+                                size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I;
+    const int j = (int)(idx - t * I);
+    const float g = gu[t * 2 * I + j], u = gu[t * 2 * I + I + j];
+    out[idx] = from_f32<act_t>((g / (1.0f + expf(-g))) * u);
+  }
+}
+
+extern "C" int TL_NAME(tl_silu_mul)(const float* gu, void* out, int T, int I, cudaStream_t stream) {
+  const size_t total = (size_t)T * I;
+  if (total == 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  silu_mul_kernel<<<blocks, 256, 0, stream>>>(gu, (act_t*)out, I, total);
+  return TL_LAUNCH_STATUS();
+}

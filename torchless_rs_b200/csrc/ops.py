@@ -1,0 +1,212 @@
+"""Python face of the CUDA launchers: argument checks, then one C call per kernel.
+
+There is no other implementation behind these functions.  A tensor that is not on
+a CUDA device, a missing library or a launch that the driver rejects raises
+`KernelError`; nothing falls back to the CPU or to library model code.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+MODE_STORE_F32 = 0
+MODE_ACCUM_F32 = 1
+MODE_SWIGLU = 2
+MODE_STORE_ACT = 3
+
+PAGE = 64  # tokens per cache page; the kernels are compiled with the same number
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
+_counter = {"launches": 0}
+
+
+def launches() -> int:
+    """Kernels launched through this module since the process started."""
+    return _counter["launches"]
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("kernel argument is not on a CUDA device; this package has no CPU path")
+    return c_void_p(t.data_ptr())
+
+
+def _check(status: int, what: str) -> None:
+    _counter["launches"] += 1
+    if status == 0:
+        return
+    if status == -1:
+        raise KernelError(f"{what}: the kernel refused its arguments")
+    if status == -2:
+        raise KernelError(f"{what}: these sizes are not supported by this kernel")
+    raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype, what: str, contiguous: bool = True) -> None:
+    if t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{what}: tensor must be contiguous")
+
+
+class CoreOps:
+    """The kernels of one activation type (float32 or bfloat16)."""
+
+    def __init__(self, act_dtype: torch.dtype):
+        if act_dtype not in _SUFFIX:
+            raise KernelError(f"no kernels for activation type {act_dtype}")
+        self.act_dtype = act_dtype
+        self.suffix = _SUFFIX[act_dtype]
+        self.lib = build.load_library(f"core_{self.suffix}")
+        for base in ("tl_embed", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
+                     "tl_gemm_generic", "tl_attn_generic"):
+            fn = getattr(self.lib, f"{base}_{self.suffix}")
+            fn.restype = c_int
+            setattr(self, "_" + base, fn)
+
+    # x[t, :] = table[tokens[t], :]
+    def embed(self, tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor) -> None:
+        _need(tokens, torch.int32, "embed tokens")
+        _need(table, self.act_dtype, "embed table")
+        _need(x, torch.float32, "embed out")
+        T, H = x.shape
+        _check(self._tl_embed(_ptr(tokens), _ptr(table), _ptr(x), c_int(T), c_int(H),
+                              c_int(table.shape[0]), _stream()), "embed")
+
+    def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> None:
+        _need(x, torch.float32, "rmsnorm in")
+        _need(out, self.act_dtype, "rmsnorm out")
+        if weight.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError(f"rmsnorm weight: unsupported dtype {weight.dtype}")
+        n_rows, H = out.shape
+        if weight.numel() != H or x.shape[1] != H:
+            raise KernelError("rmsnorm: sizes do not match")
+        if rows is not None:
+            _need(rows, torch.int32, "rmsnorm rows")
+        _check(self._tl_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight),
+                                c_int(1 if weight.dtype == torch.float32 else 0), _ptr(out),
+                                c_int(n_rows), c_int(H), c_float(eps), _stream()), "rmsnorm")
+
+    def rope_cache_write(self, qkv: torch.Tensor, q_out: torch.Tensor,
+                         k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                         token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+                         page_table: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                         style: int, nh: int, nkv: int, hd: int) -> None:
+        _need(qkv, torch.float32, "rope qkv")
+        _need(q_out, self.act_dtype, "rope q out")
+        T = qkv.shape[0]
+        stride = 0
+        if k_pages is not None:
+            _need(k_pages, self.act_dtype, "k pages")
+            _need(v_pages, self.act_dtype, "v pages")
+            _need(page_table, torch.int32, "page table")
+            stride = page_table.stride(0)
+            if qkv.shape[1] < (nh + 2 * nkv) * hd:
+                raise KernelError("rope: qkv has too few columns")
+        if inv_freq is not None:
+            _need(inv_freq, torch.float32, "inv_freq")
+            if inv_freq.numel() != hd // 2:
+                raise KernelError("rope: inv_freq must have head_dim/2 entries")
+        _check(self._tl_rope_cache_write(
+            _ptr(qkv), c_int(qkv.stride(0)), _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
+            _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), c_int(stride),
+            _ptr(inv_freq), c_int(style), c_int(T), c_int(nh), c_int(nkv), c_int(hd), _stream()),
+            "rope_cache_write")
+
+    def silu_mul(self, gu: torch.Tensor, out: torch.Tensor) -> None:
+        _need(gu, torch.float32, "silu_mul in")
+        _need(out, self.act_dtype, "silu_mul out")
+        T, I = out.shape
+        _check(self._tl_silu_mul(_ptr(gu), _ptr(out), c_int(T), c_int(I), _stream()), "silu_mul")
+
+    def gemm_generic(self, a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, mode: int) -> None:
+        """c (op)= a @ w.T; in SwiGLU mode w holds the gate rows, then the up rows."""
+        _need(a, self.act_dtype, "gemm a", contiguous=False)
+        _need(w, self.act_dtype, "gemm w", contiguous=False)
+        want_c = torch.float32 if mode in (MODE_STORE_F32, MODE_ACCUM_F32) else self.act_dtype
+        _need(c, want_c, "gemm c", contiguous=False)
+        M, K = a.shape
+        N = c.shape[1]
+        rows_w = 2 * N if mode == MODE_SWIGLU else N
+        if w.shape != (rows_w, K) or c.shape[0] != M:
+            raise KernelError(f"gemm: shapes do not fit: a {tuple(a.shape)} w {tuple(w.shape)} "
+                              f"c {tuple(c.shape)} mode {mode}")
+        if a.stride(1) != 1 or w.stride(1) != 1 or c.stride(1) != 1:
+            raise KernelError("gemm: the last dimension must be contiguous")
+        _check(self._tl_gemm_generic(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)),
+                                     _ptr(c), c_int(c.stride(0)), c_int(M), c_int(N), c_int(K),
+                                     c_int(mode), _stream()), "gemm_generic")
+
+    def attn_generic(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     out: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+                     seq_slot: torch.Tensor, page_table: torch.Tensor, nh: int, nkv: int, hd: int,
+                     window: Optional[int], scale: float) -> None:
+        for t, n in ((q, "attn q"), (k_pages, "k pages"), (v_pages, "v pages"), (out, "attn out")):
+            _need(t, self.act_dtype, n)
+        _need(page_table, torch.int32, "page table")
+        T = q.shape[0]
+        _check(self._tl_attn_generic(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(token_pos), _ptr(token_seq),
+            _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)), c_int(T), c_int(nh),
+            c_int(nkv), c_int(hd), c_int(window or 0), c_float(scale), _stream()), "attn_generic")
+
+
+class SamplingOps:
+    def __init__(self):
+        self.lib = build.load_library("sampling")
+        self.lib.tl_argmax.restype = c_int
+        self.lib.tl_sample.restype = c_int
+
+    def argmax(self, logits: torch.Tensor, out: torch.Tensor) -> None:
+        _need(logits, torch.float32, "argmax logits", contiguous=False)
+        _need(out, torch.int32, "argmax out")
+        rows, V = logits.shape
+        if logits.stride(1) != 1:
+            raise KernelError("argmax: the last dimension must be contiguous")
+        _check(self.lib.tl_argmax(_ptr(logits), c_int(logits.stride(0)), c_int(rows), c_int(V),
+                                  _ptr(out), _stream()), "argmax")
+
+    def sample(self, logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
+               uniform: torch.Tensor, out: torch.Tensor) -> None:
+        _need(logits, torch.float32, "sample logits", contiguous=False)
+        _need(uniform, torch.float32, "sample uniform")
+        _need(out, torch.int32, "sample out")
+        rows, V = logits.shape
+        if logits.stride(1) != 1 or uniform.numel() < rows or out.numel() < rows:
+            raise KernelError("sample: bad arguments")
+        _check(self.lib.tl_sample(_ptr(logits), c_int(logits.stride(0)), c_int(rows), c_int(V),
+                                  c_float(temperature), c_int(top_k), c_float(top_p),
+                                  _ptr(uniform), _ptr(out), _stream()), "sample")
+
+
+_core: dict = {}
+_sampling: list = []
+
+
+def core_ops(act_dtype: torch.dtype) -> CoreOps:
+    if act_dtype not in _core:
+        _core[act_dtype] = CoreOps(act_dtype)
+    return _core[act_dtype]
+
+
+def sampling_ops() -> SamplingOps:
+    if not _sampling:
+        _sampling.append(SamplingOps())
+    return _sampling[0]

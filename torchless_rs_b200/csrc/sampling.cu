@@ -1,0 +1,333 @@
+// Token selection on the device: arg-max, and sampling with temperature, top-k and
+// top-p in the order of the reference (src/sampler/mod.rs:194-222): logits / T, top-k
+// on the scaled logits, softmax, top-p on the probabilities, inverse-CDF draw.
+//
+// One block per row of logits.  Probabilities are kept as 40-bit fixed-point
+// integers of exp(z - max): integer sums do not depend on the order of addition, so
+// every threshold and the draw are the same from run to run and equal to a
+// sequential pass in index order.  The uniform number of each row comes from the
+// host, which derives it from (seed, sequence, step).
+//
+// Ties: arg-max keeps the lowest index (the reference's max_by keeps the last,
+// src/sampler/mod.rs:60-68); at a top-k or top-p threshold the tied entries of lowest
+// index are kept (top-k: as the reference, :108-117; top-p: the reference's unstable
+// sort leaves it open, :147).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SAMPLE_THREADS 1024
+#define FIX_ONE 1099511627776.0f  // 2^40
+
+typedef unsigned long long u64;
+
+__device__ __forceinline__ uint32_t float_key(float f) {
+  // larger float -> larger key; NaN is pushed below everything
+  if (f != f) return 0u;
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// --------------------------------------------------------------------------
+// arg-max
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+  __shared__ uint32_t sk[32];
+  __shared__ int si[32];
+  const float* row = logits + (size_t)blockIdx.x * ld;
+  uint32_t best = 0u;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const uint32_t k = float_key(row[i]);
+    if (k > best || (k == best && i < best_i)) { best = k; best_i = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const uint32_t ok = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ok > best || (ok == best && oi < best_i)) { best = ok; best_i = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sk[warp] = best; si[warp] = best_i; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best = lane < nw ? sk[lane] : 0u;
+    best_i = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const uint32_t ok = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ok > best || (ok == best && oi < best_i)) { best = ok; best_i = oi; }
+    }
+    if (lane == 0) out[blockIdx.x] = best_i < V ? best_i : 0;
+  }
+}
+
+extern "C" int tl_argmax(const float* logits, int ld, int rows, int V, int* out,
+                         cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (V <= 0) return -1;
+  argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, out);
+  return (int)cudaGetLastError();
+}
+
+// --------------------------------------------------------------------------
+// sampling
+// --------------------------------------------------------------------------
+struct SampleShared {
+  u64 wsum[256];
+  uint32_t cnt[256];
+  u64 warp_tot[32];
+  float red[33];
+  u64 bcast_u64[2];
+  int bcast_int[2];
+};
+
+__device__ __forceinline__ float blk_max(float v, SampleShared& sm) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) sm.red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < (int)(blockDim.x >> 5) ? sm.red[lane] : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+    if (lane == 0) sm.red[32] = t;
+  }
+  __syncthreads();
+  return sm.red[32];
+}
+
+// Inclusive scan of one value per thread over the block, in thread order.
+// Returns the inclusive prefix; *total receives the block total.
+__device__ __forceinline__ u64 blk_scan(u64 v, SampleShared& sm, u64* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const u64 n = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += n;
+  }
+  __syncthreads();
+  if (lane == 31) sm.warp_tot[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    u64 t = lane < (int)(blockDim.x >> 5) ? sm.warp_tot[lane] : 0ull;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const u64 n = __shfl_up_sync(0xffffffffu, t, o);
+      if (lane >= o) t += n;
+    }
+    sm.warp_tot[lane] = t;  // inclusive totals of the warps
+  }
+  __syncthreads();
+  const u64 off = warp ? sm.warp_tot[warp - 1] : 0ull;
+  *total = sm.warp_tot[(blockDim.x >> 5) - 1];
+  return v + off;
+}
+
+struct RowView {
+  const float* row;
+  int V;
+  float T;
+  float m;            // max of z
+  // top-k state
+  bool use_k;
+  uint32_t k_thr;     // key of the k-th largest z
+  int k_cut;          // entries equal to k_thr are kept up to this index
+  // top-p state
+  bool use_p;
+  u64 p_thr;
+  int p_cut;
+};
+
+__device__ __forceinline__ float z_of(const RowView& rv, int i) { return rv.row[i] / rv.T; }
+
+__device__ __forceinline__ bool kept_k(const RowView& rv, float z, int i) {
+  if (!rv.use_k) return true;
+  const uint32_t k = float_key(z);
+  return k > rv.k_thr || (k == rv.k_thr && i <= rv.k_cut);
+}
+
+__device__ __forceinline__ u64 fix_of(const RowView& rv, float z) {
+  return (u64)(expf(z - rv.m) * FIX_ONE);
+}
+
+// Index of the `need`-th entry (1-based, in index order) for which pred holds.
+template <typename Pred>
+__device__ int nth_in_order(int V, int need, SampleShared& sm, Pred pred) {
+  u64 carry = 0;
+  int found = V - 1;
+  for (int base = 0; base < V; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const u64 f = (i < V && pred(i)) ? 1ull : 0ull;
+    u64 total;
+    const u64 inc = blk_scan(f, sm, &total) + carry;
+    if (f && inc == (u64)need) sm.bcast_int[0] = i;
+    const bool done = carry < (u64)need && carry + total >= (u64)need;
+    carry += total;
+    __syncthreads();
+    if (done) { found = sm.bcast_int[0]; break; }
+  }
+  __syncthreads();
+  return found;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature, int top_k,
+              float top_p, const float* __restrict__ uniform, int* __restrict__ out) {
+  __shared__ SampleShared sm;
+  const int tid = threadIdx.x;
+  RowView rv;
+  rv.row = logits + (size_t)blockIdx.x * ld;
+  rv.V = V;
+  rv.T = temperature;
+  rv.use_k = top_k > 0 && top_k < V;
+  rv.use_p = top_p > 0.0f && top_p < 1.0f;
+  rv.k_thr = 0u; rv.k_cut = V; rv.p_thr = 0ull; rv.p_cut = V;
+
+  // ---- max of the scaled logits
+  float m = -INFINITY;
+  for (int i = tid; i < V; i += blockDim.x) {
+    const float z = z_of(rv, i);
+    if (z == z) m = fmaxf(m, z);
+  }
+  rv.m = blk_max(m, sm);
+
+  // ---- top-k: key of the k-th largest scaled logit by radix selection
+  if (rv.use_k) {
+    uint32_t prefix = 0u, mask = 0u;
+    int remaining = top_k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int b = tid; b < 256; b += blockDim.x) sm.cnt[b] = 0u;
+      __syncthreads();
+      for (int i = tid; i < V; i += blockDim.x) {
+        const uint32_t k = float_key(z_of(rv, i));
+        if ((k & mask) == prefix) atomicAdd(&sm.cnt[(k >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        int rem = remaining, b = 255;
+        for (; b > 0; --b) {
+          if ((int)sm.cnt[b] >= rem) break;
+          rem -= (int)sm.cnt[b];
+        }
+        sm.bcast_int[0] = b;
+        sm.bcast_int[1] = rem;
+      }
+      __syncthreads();
+      prefix |= ((uint32_t)sm.bcast_int[0]) << shift;
+      mask |= 255u << shift;
+      remaining = sm.bcast_int[1];
+      __syncthreads();
+    }
+    rv.k_thr = prefix;
+    // `remaining` entries equal to the threshold are kept, lowest indices first
+    const uint32_t thr = prefix;
+    const RowView rvc = rv;
+    rv.k_cut = nth_in_order(V, remaining, sm,
+                            [&](int i) { return float_key(z_of(rvc, i)) == thr; });
+  }
+
+  // ---- sum of the kept fixed-point weights
+  u64 part = 0;
+  for (int i = tid; i < V; i += blockDim.x) {
+    const float z = z_of(rv, i);
+    if (z == z && kept_k(rv, z, i)) part += fix_of(rv, z);
+  }
+  u64 S;
+  blk_scan(part, sm, &S);
+  __syncthreads();
+
+  // ---- top-p: smallest weight that still belongs to the nucleus
+  if (rv.use_p) {
+    u64 target = (u64)ceil((double)top_p * (double)S);
+    if (target > S) target = S;
+    if (target < 1ull) target = 1ull;
+    u64 prefix = 0ull, mask = 0ull, above = 0ull;  // `above` = weight strictly above the prefix
+    for (int shift = 40; shift >= 0; shift -= 8) {
+      for (int b = tid; b < 256; b += blockDim.x) { sm.cnt[b] = 0u; sm.wsum[b] = 0ull; }
+      __syncthreads();
+      for (int i = tid; i < V; i += blockDim.x) {
+        const float z = z_of(rv, i);
+        if (!(z == z) || !kept_k(rv, z, i)) continue;
+        const u64 w = fix_of(rv, z);
+        if ((w & mask) == prefix) {
+          const int b = (int)((w >> shift) & 255ull);
+          atomicAdd(&sm.cnt[b], 1u);
+          atomicAdd(&sm.wsum[b], w);
+        }
+      }
+      __syncthreads();
+      if (tid == 0) {
+        u64 acc = above;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (acc + sm.wsum[b] >= target) break;
+          acc += sm.wsum[b];
+        }
+        sm.bcast_int[0] = b;
+        sm.bcast_u64[0] = acc;
+      }
+      __syncthreads();
+      prefix |= ((u64)sm.bcast_int[0]) << shift;
+      mask |= 255ull << shift;
+      above = sm.bcast_u64[0];
+      __syncthreads();
+    }
+    rv.p_thr = prefix;
+    int need = 1;
+    if (prefix > 0ull && target > above) {
+      const u64 n = (target - above + prefix - 1ull) / prefix;
+      need = n > (u64)V ? V : (int)n;
+      if (need < 1) need = 1;
+    }
+    const RowView rvc = rv;
+    const u64 thr = prefix;
+    rv.p_cut = nth_in_order(V, need, sm, [&](int i) {
+      const float z = z_of(rvc, i);
+      return z == z && kept_k(rvc, z, i) && fix_of(rvc, z) == thr;
+    });
+    S = above + (u64)need * prefix;
+  }
+
+  // ---- draw: first kept index whose running weight exceeds floor(r * S)
+  float r = uniform[blockIdx.x];
+  r = r < 0.0f ? 0.0f : (r >= 1.0f ? 0.99999994f : r);
+  u64 target = (u64)((double)r * (double)S);
+  if (target >= S) target = S ? S - 1ull : 0ull;
+  u64 carry = 0;
+  int chosen = -1;
+  for (int base = 0; base < V; base += blockDim.x) {
+    const int i = base + tid;
+    u64 w = 0;
+    if (i < V) {
+      const float z = z_of(rv, i);
+      if (z == z && kept_k(rv, z, i)) {
+        w = fix_of(rv, z);
+        if (rv.use_p && !(w > rv.p_thr || (w == rv.p_thr && i <= rv.p_cut))) w = 0;
+      }
+    }
+    u64 total;
+    const u64 inc = blk_scan(w, sm, &total) + carry;
+    if (w && inc > target && inc - w <= target) sm.bcast_int[0] = i;
+    const bool done = carry + total > target;
+    carry += total;
+    __syncthreads();
+    if (done) { chosen = sm.bcast_int[0]; break; }
+  }
+  if (tid == 0) out[blockIdx.x] = chosen >= 0 ? chosen : V - 1;  // the reference's fallback, :237
+}
+
+// temperature must be > 0; rows with temperature <= 0 go through tl_argmax.
+extern "C" int tl_sample(const float* logits, int ld, int rows, int V, float temperature,
+                         int top_k, float top_p, const float* uniform, int* out,
+                         cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (V <= 0 || !(temperature > 0.0f)) return -1;
+  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p,
+                                                     uniform, out);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,103 @@
+"""The tokens of one step and where they belong, as the kernels read them."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepBatch:
+    """Packed tokens of all sequences of a step, sequence after sequence.
+
+    Device tensors (int32): `tokens` [T]; `token_seq` [T], the batch row of each
+    token; `token_pos` [T], its position in its sequence; `seq_slot` [B], the cache
+    slot of each row; `seq_start` [B+1], offsets of the rows in the packed tokens;
+    `seq_len` [B], each sequence's length after this step; `want_rows` [R], packed
+    indices whose logits are wanted."""
+    n_tokens: int
+    n_seqs: int
+    n_want: int
+    is_decode: bool
+    max_new: int
+    max_len: int
+    tokens: torch.Tensor
+    token_seq: torch.Tensor
+    token_pos: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_start: torch.Tensor
+    seq_len: torch.Tensor
+    want_rows: torch.Tensor
+    slots: List[int]
+    past_lens: List[int]
+    new_lens: List[int]
+
+
+def layout_step(past_lens: Sequence[int], counts: Sequence[int], slots: Sequence[int],
+                tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]]) -> dict:
+    """Host arithmetic of a step as numpy arrays (no device needed)."""
+    B = len(slots)
+    T = int(sum(counts))
+    seq_start = np.zeros(B + 1, dtype=np.int32)
+    seq_start[1:] = np.cumsum(counts)
+    token_seq = np.repeat(np.arange(B, dtype=np.int32), counts)
+    token_pos = np.concatenate(
+        [np.arange(p, p + c, dtype=np.int32) for p, c in zip(past_lens, counts)]
+    ) if T else np.zeros(0, dtype=np.int32)
+    toks = np.concatenate([np.asarray(t, dtype=np.int64) for t in tokens]) if T else np.zeros(0, dtype=np.int64)
+    want_rows = []
+    for b, w in enumerate(want):
+        for i in w:
+            if not 0 <= i < counts[b]:
+                raise ValueError(f"wanted place {i} lies outside the {counts[b]} tokens of entry {b}")
+            want_rows.append(int(seq_start[b]) + int(i))
+    return dict(
+        tokens=toks.astype(np.int32), token_seq=token_seq, token_pos=token_pos,
+        seq_slot=np.asarray(slots, dtype=np.int32), seq_start=seq_start,
+        seq_len=np.asarray([p + c for p, c in zip(past_lens, counts)], dtype=np.int32),
+        want_rows=np.asarray(want_rows, dtype=np.int32))
+
+
+class BatchStager:
+    """Packs a step's arrays into one pinned host buffer and brings them to the
+    device with one copy.  The device buffer keeps its address, so views taken for
+    the same sizes stay valid from step to step."""
+
+    FIELDS = ("tokens", "token_seq", "token_pos", "seq_slot", "seq_start", "seq_len", "want_rows")
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.capacity = 0
+        self.host: Optional[torch.Tensor] = None
+        self.dev: Optional[torch.Tensor] = None
+
+    def _ensure(self, n: int) -> None:
+        if n <= self.capacity:
+            return
+        cap = max(4096, 1 << (n - 1).bit_length())
+        self.host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self.capacity = cap
+
+    def stage(self, arrays: dict, slots, past_lens, is_decode: bool) -> StepBatch:
+        sizes = [int(arrays[f].shape[0]) for f in self.FIELDS]
+        # every field starts on a 4-element (16-byte) boundary
+        offs, total = [], 0
+        for s in sizes:
+            offs.append(total)
+            total += (s + 3) // 4 * 4
+        self._ensure(max(total, 1))
+        hv = self.host.numpy()
+        for f, o, s in zip(self.FIELDS, offs, sizes):
+            hv[o:o + s] = arrays[f]
+        self.dev[:total].copy_(self.host[:total], non_blocking=True)
+        views = {f: self.dev[o:o + s] for f, o, s in zip(self.FIELDS, offs, sizes)}
+        counts = np.diff(arrays["seq_start"])
+        return StepBatch(
+            n_tokens=sizes[0], n_seqs=sizes[3], n_want=sizes[6], is_decode=is_decode,
+            max_new=int(counts.max()) if len(counts) else 0,
+            max_len=int(arrays["seq_len"].max()) if sizes[5] else 0,
+            slots=list(slots), past_lens=list(past_lens),
+            new_lens=[int(x) for x in arrays["seq_len"]], **views)

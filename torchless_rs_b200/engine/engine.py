@@ -1,0 +1,84 @@
+"""The step function: one batch of sequences, the tokens it is given, from the cache.
+
+The reference's forward takes one token of one sequence and the caller advances
+the position (src/model/mod.rs:430-468, src/main.rs:557-563).  Here a step takes a
+batch whose sequences either all start (prompts of unequal lengths, run together
+as one packed batch) or all go on by one token; positions come from the cache's
+record of each sequence and advance inside the step."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..cache import Cache
+from ..config.spec import ModelSpec
+from ..parts.runtime import Runtime
+from .batch import BatchStager, StepBatch, layout_step
+from .model import DecoderModel
+
+
+class Engine:
+    """Owns the model, its cache and the staging of steps.
+
+    `max_tokens`: the most tokens that live sequences hold at any time, each
+    sequence's count rounded up to a multiple of 64; it sizes the cache."""
+
+    def __init__(self, spec: ModelSpec, weights, rt: Runtime, max_tokens: int,
+                 max_batch: Optional[int] = None, max_seq_len: Optional[int] = None):
+        self.spec = spec
+        self.rt = rt
+        self.model = DecoderModel(spec, rt)
+        self.model.load(weights)
+        self.cache = Cache(self.model.cache_requests(), max_tokens, max_batch, max_seq_len,
+                           dtype=rt.act_dtype, device=rt.device)
+        self.model.bind_cache(self.cache)
+        self.stager = BatchStager(rt.device)
+        self.vocab_size = spec.vocab_size
+
+    # ---- sequences -------------------------------------------------------------------
+    def start_sequences(self, count: int) -> List[int]:
+        """Takes `count` free slots; each stands for a new, empty sequence."""
+        return self.cache.acquire(count)
+
+    def end_sequences(self, slots: Sequence[int]) -> None:
+        """Gives the slots and everything they hold back."""
+        self.cache.release(slots)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ----------------------------------------------------------------------
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Union[str, Sequence[Sequence[int]]] = "last") -> Optional[torch.Tensor]:
+        """Runs `tokens[b]` as the next tokens of the sequence in `slots[b]` and
+        returns the 32-bit logits [wanted, vocab] on the device, in the order of the
+        sequences and of their wanted places (`want[b]`: indices into `tokens[b]`;
+        "last": the last token of each; "all"; "none").  The returned tensor is a
+        view of a buffer that the next step overwrites."""
+        B = len(slots)
+        if B == 0:
+            return None
+        if len(tokens) != B:
+            raise ValueError("one token list per slot is needed")
+        counts = [len(t) for t in tokens]
+        if min(counts) < 1:
+            raise ValueError("every sequence of a step brings at least one token")
+        if want == "last":
+            want = [[c - 1] for c in counts]
+        elif want == "all":
+            want = [list(range(c)) for c in counts]
+        elif want == "none" or want is None:
+            want = [[] for _ in counts]
+        past = [self.cache.length(s) for s in slots]
+        arrays = layout_step(past, counts, slots, tokens, want)
+        toks = arrays["tokens"]
+        if toks.size and (toks.min() < 0 or toks.max() >= self.vocab_size):
+            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
+        new_lens = [p + c for p, c in zip(past, counts)]
+        self.cache.prepare(slots, new_lens)
+        batch = self.stager.stage(arrays, slots, past, is_decode=all(c == 1 for c in counts))
+        logits = self.model.forward(batch)
+        self.cache.commit(slots, new_lens)
+        return logits
