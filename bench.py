@@ -1,0 +1,301 @@
+"""Measurement of decode and prefill throughput at Mistral-7B sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints one JSON line.  A "step" is one decode step of the whole batch.  The default
+run: random weights of the sizes of Mistral-7B-v0.1, batch 8, every sequence ending
+at a context of 4096 tokens.  `value` is decoded tokens per second timed on the device
+(CUDA events around K steps of step + token selection); `e2e` is the same through the
+Python entry point `Model.generate`, host token ids in and out each step, timed by
+the host between the first and the last emitted token.  Inputs exceed the L2 cache
+(14 GB of weights are read each step), so no flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+_ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, _ROOT)
+
+# BASELINE.json configs[2]
+MISTRAL_7B = dict(
+    architectures=["MistralForCausalLM"], model_type="mistral", num_hidden_layers=32,
+    hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    intermediate_size=14336, vocab_size=32000, rope_theta=10000.0, sliding_window=4096,
+    rms_norm_eps=1e-5, max_position_embeddings=32768, tie_word_embeddings=False)
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks() -> dict:
+    p = os.path.join(_ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        with open(p) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def mark(self):
+        return time.time()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, t0: float, t1: float) -> dict:
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 6] or \
+               [r for _, r in self.rows if len(r) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower() == "active" for r in rows)]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None,
+                "sm_max_mhz": float(rows[0][1]) if rows[0][1].replace(".", "").isdigit() else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def weight_bytes_per_step(cfg: dict, n_layers: int, elt: int = 2) -> int:
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = ((nh + 2 * nkv) * hd * H + nh * hd * H + 3 * I * H + 2 * H) * elt
+    return n_layers * per_layer + (V * H + H) * elt
+
+
+def kv_bytes_per_token(cfg: dict, n_layers: int, elt: int = 2) -> int:
+    return 2 * n_layers * cfg["num_key_value_heads"] * cfg["head_dim"] * elt
+
+
+def prefill_flops(cfg: dict, n_layers: int, n: int) -> float:
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nh + 2 * nkv) * hd * H + nh * hd * H + 3 * I * H
+    return 2.0 * n * per_layer * n_layers + 2.0 * nh * hd * n * n * n_layers + 2.0 * V * H
+
+
+def fill_context(model, batch: int, context: int):
+    """Takes `batch` slots and gives each a context of `context` tokens of synthetic
+    cache content (random keys and values), without running a prefill."""
+    import torch
+    eng = model.engine
+    slots = eng.start_sequences(batch)
+    lens = [context] * batch
+    eng.cache.prepare(slots, lens)
+    eng.cache.commit(slots, lens)
+    return slots
+
+
+def decode_device_timed(model, batch: int, steps: int, warmup: int, end_context: int):
+    """K decode steps (step + greedy selection) timed with CUDA events; the sequences
+    end at `end_context` tokens.  Returns (tokens/s, ms per step, mean context,
+    launches in the timed region)."""
+    import torch
+    from torchless_rs_b200.csrc import ops
+    from torchless_rs_b200.sampling.params import SamplingParams
+    eng = model.engine
+    start = end_context - steps - warmup
+    slots = fill_context(model, batch, start)
+    toks = [[(7 * i + 3) % eng.vocab_size] for i in range(batch)]
+    greedy = SamplingParams.greedy()
+    for _ in range(warmup):
+        model.sampler.select(eng.step(slots, toks, "last"), greedy)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = ops.launches()
+    e0.record()
+    for _ in range(steps):
+        model.sampler.select(eng.step(slots, toks, "last"), greedy)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = ops.launches() - l0
+    eng.end_sequences(slots)
+    mean_ctx = end_context - steps / 2.0
+    return batch / (ms / 1e3), ms, mean_ctx, launches
+
+
+def decode_end_to_end(model, batch: int, steps: int, warmup: int, end_context: int):
+    """The same through `Model.generate`: host token ids in, host token ids out at
+    every step.  The context is put in place first; the time runs from the first
+    emitted token (after the one-token 'prompt' step and warm-up) to the last."""
+    import torch
+    eng = model.engine
+    start = end_context - steps - warmup - 1
+    slots = fill_context(model, batch, start)
+    # generate() takes its own slots; hand it sequences that already hold a context by
+    # wrapping the engine's start_sequences for this one call
+    stamps = []
+    taken = {"done": False}
+    orig = eng.start_sequences
+
+    def start_sequences(count):
+        assert count == batch and not taken["done"]
+        taken["done"] = True
+        return slots
+    eng.start_sequences = start_sequences
+    try:
+        prompts = [[(11 * i + 5) % eng.vocab_size] for i in range(batch)]
+        def on_token(i, tok):
+            if i == batch - 1:
+                torch.cuda.synchronize()
+                stamps.append(time.perf_counter())
+        model.generate(prompts, max_tokens=steps + warmup + 1, temperature=0.0, stop_ids=(),
+                       on_token=on_token)
+    finally:
+        eng.start_sequences = orig
+    dt = stamps[-1] - stamps[warmup]
+    n = len(stamps) - 1 - warmup
+    return batch * n / dt, 1e3 * dt / n
+
+
+def prefill_timed(model, n_tokens: int, repeats: int = 3):
+    import torch
+    eng = model.engine
+    toks = [[(13 * i + 1) % eng.vocab_size for i in range(n_tokens)]]
+    best = None
+    for r in range(repeats + 1):
+        (s,) = eng.start_sequences(1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([s], toks, "last")
+        e1.record()
+        torch.cuda.synchronize()
+        eng.end_sequences([s])
+        ms = e0.elapsed_time(e1)
+        if r > 0:
+            best = ms if best is None else min(best, ms)
+    return best
+
+
+def reference_arm(args) -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "rglonek/torchless-rs is a Rust crate (Cargo.toml, no Python package "
+                       "metadata); pip cannot install it offline and no cargo/rustc exists here"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than the configuration has (named in the record)")
+    ap.add_argument("--batch", type=int, default=8)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torchless_rs_b200 as tl
+    from torchless_rs_b200.config import config_from_dict
+
+    peaks = load_peaks()
+    cfg = dict(MISTRAL_7B)
+    full_layers = cfg["num_hidden_layers"]
+    n_layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = n_layers
+    config = config_from_dict(cfg)
+    B = args.batch
+    big = max(B, 64)
+    model = tl.from_random(config, seed=0, dtype="bfloat16", max_tokens=big * CONTEXT,
+                           max_batch=big, max_seq_len=CONTEXT)
+    for g in model.engine.cache.paged:   # synthetic cache content
+        g.storage.normal_(0.0, 0.5)
+    wbytes = weight_bytes_per_step(cfg, n_layers)
+    kvb = kv_bytes_per_token(cfg, n_layers)
+
+    clocks = ClockSampler()
+    clocks.start()
+    time.sleep(0.3)
+    t0 = clocks.mark()
+    tps, ms, mean_ctx, launches = decode_device_timed(model, B, args.steps, args.warmup, CONTEXT)
+    t1 = clocks.mark()
+    e2e_tps, e2e_ms = decode_end_to_end(model, B, args.steps, args.warmup, CONTEXT)
+    points = {}
+    for b, k in ((1, min(args.steps, 32)), (64, min(args.steps, 16))):
+        p_tps, p_ms, _, _ = decode_device_timed(model, b, k, 3, CONTEXT)
+        points[f"decode_b{b}"] = round(p_tps, 1)
+        points[f"decode_b{b}_ms"] = round(p_ms, 3)
+    pre_ms = prefill_timed(model, PREFILL_TOKENS)
+    clocks.stop()
+
+    step_bytes = wbytes + B * mean_ctx * kvb
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+    rec = {
+        "metric": "decode tok/s (Mistral 7B sizes, bf16, batch 8, context 4096)",
+        "value": round(tps, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), random cache content, fixed token ids",
+        "impl": "ours",
+        "config": {
+            "model": "Mistral-7B-v0.1 sizes", "layers": n_layers, "layers_of_config": full_layers,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "sliding_window": cfg["sliding_window"], "rope_theta": cfg["rope_theta"],
+            "global_batch": B, "seq_len": CONTEXT, "mean_context": mean_ctx,
+            "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
+            "l2": "inputs_exceed_l2", "peaks": peaks["source"],
+        },
+        "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": 4 * (4 * ((B + 3) // 4 * 4) + 2 * ((B + 4) // 4 * 4) + 4),
+                "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(t0, t1),
+    }
+    print(json.dumps(rec))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
