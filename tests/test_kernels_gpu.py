@@ -1,0 +1,281 @@
+"""Each kernel alone against a plain 32-bit reference written here, at sizes other
+than the engine tests use."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+PAGE = 64
+
+
+def _ops(dtype):
+    from torchless_rs_b200.csrc import ops
+    return ops.core_ops(dtype)
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ---------------------------------------------------------------------------
+# embedding, norm, SiLU-gate
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    o = _ops(dtype)
+    table = _rand((301, 72), dtype, 1)
+    toks = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    x = torch.empty((5, 72), dtype=torch.float32, device=DEV)
+    o.embed(toks, table, x)
+    assert torch.equal(x, table[toks.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,eps", [(72, 1e-5), (4096, 1e-6), (1000, 3e-3)])
+def test_rmsnorm(dtype, H, eps):
+    o = _ops(dtype)
+    x = _rand((7, H), torch.float32, 2, 3.0)
+    for wdt in (torch.float32, torch.bfloat16):
+        w = (1 + 0.1 * _rand((H,), torch.float32, 3)).to(wdt)
+        y = torch.empty((7, H), dtype=dtype, device=DEV)
+        o.rmsnorm(x, w, eps, y)
+        xd = x.double()
+        ref = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps) * w.double()
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        assert torch.allclose(y.double(), ref, rtol=tol, atol=tol)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    y = torch.empty((3, H), dtype=dtype, device=DEV)
+    o.rmsnorm(x, w, eps, y, rows)
+    full = torch.empty((7, H), dtype=dtype, device=DEV)
+    o.rmsnorm(x, w, eps, full)
+    assert torch.equal(y, full[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    o = _ops(dtype)
+    gu = _rand((5, 2 * 177), torch.float32, 4, 3.0)
+    out = torch.empty((5, 177), dtype=dtype, device=DEV)
+    o.silu_mul(gu, out)
+    g, u = gu[:, :177].double(), gu[:, 177:].double()
+    ref = g / (1 + torch.exp(-g)) * u
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    assert torch.allclose(out.double(), ref, rtol=tol, atol=tol)
+
+
+# ---------------------------------------------------------------------------
+# matrix products on CUDA cores: every mode, skinny and tiled, odd sizes
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 50, 33), (3, 129, 72), (8, 64, 4096), (9, 65, 100),
+                                   (70, 200, 177), (130, 31, 64)])
+def test_gemm_generic(dtype, M, N, K):
+    from torchless_rs_b200.csrc import ops
+    o = _ops(dtype)
+    a = _rand((M, K), dtype, 5)
+    w = _rand((2 * N, K), dtype, 6, 1.0 / math.sqrt(K))   # products of size ~1
+    ad, wd = a.double(), w.double()
+    ref = ad @ wd[:N].T
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    c = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    o.gemm_generic(a, w[:N], c, ops.MODE_STORE_F32)
+    assert torch.allclose(c.double(), ref, rtol=1e-5, atol=1e-4)
+    base = _rand((M, N), torch.float32, 7)
+    c2 = base.clone()
+    o.gemm_generic(a, w[:N], c2, ops.MODE_ACCUM_F32)
+    assert torch.allclose(c2.double(), base.double() + ref, rtol=1e-5, atol=1e-4)
+    c3 = torch.empty((M, N), dtype=dtype, device=DEV)
+    o.gemm_generic(a, w[:N], c3, ops.MODE_STORE_ACT)
+    assert torch.allclose(c3.double(), ref, **tol)
+    c4 = torch.empty((M, N), dtype=dtype, device=DEV)
+    o.gemm_generic(a, w, c4, ops.MODE_SWIGLU)
+    up = ad @ wd[N:].T
+    assert torch.allclose(c4.double(), ref / (1 + torch.exp(-ref)) * up, **tol)
+
+
+# ---------------------------------------------------------------------------
+# paged cache helpers and a plain attention reference
+# ---------------------------------------------------------------------------
+class Paged:
+    """Dense keys and values of several sequences laid into shuffled cache pages."""
+
+    def __init__(self, lens, nkv, hd, dtype, seed, poison=True):
+        self.lens, self.nkv, self.hd = list(lens), nkv, hd
+        B = len(lens)
+        g = torch.Generator().manual_seed(seed)
+        self.k = [torch.randn((n, nkv, hd), generator=g).to(dtype) for n in lens]
+        self.v = [torch.randn((n, nkv, hd), generator=g).to(dtype) for n in lens]
+        need = sum((n + PAGE - 1) // PAGE for n in lens)
+        n_pages = need + 3
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        width = max((n + PAGE - 1) // PAGE for n in lens) + 1
+        self.n_slots = B + 2
+        self.slots = torch.randperm(self.n_slots, generator=g).tolist()[:B]
+        assert len(set(self.slots)) == B
+        table = torch.full((self.n_slots, width), -1, dtype=torch.int32)
+        fill = 1e4 if poison else 0.0   # unused rows hold large finite numbers
+        kp = torch.full((n_pages, nkv, PAGE, hd), fill).to(dtype)
+        vp = torch.full((n_pages, nkv, hd, PAGE), fill).to(dtype)
+        it = iter(perm)
+        for b, n in enumerate(lens):
+            for j in range((n + PAGE - 1) // PAGE):
+                p = next(it)
+                table[self.slots[b], j] = p
+                cnt = min(PAGE, n - j * PAGE)
+                kp[p, :, :cnt, :] = self.k[b][j * PAGE:j * PAGE + cnt].permute(1, 0, 2)
+                vp[p, :, :, :cnt] = self.v[b][j * PAGE:j * PAGE + cnt].permute(1, 2, 0)
+        self.k_pages, self.v_pages = kp.to(DEV), vp.to(DEV)
+        self.table = table.to(DEV)
+        self.seq_slot = torch.tensor(self.slots, dtype=torch.int32, device=DEV)
+
+
+def attention_reference(q, k, v, pos, window, scale):
+    """q [nh, hd] at position `pos` over k, v [n, nkv, hd]; float64."""
+    nh, hd = q.shape
+    nkv = k.shape[1]
+    lo = max(0, pos - window + 1) if window else 0
+    out = torch.empty((nh, hd), dtype=torch.float64)
+    for h in range(nh):
+        kk = k[lo:pos + 1, h // (nh // nkv)].double()
+        vv = v[lo:pos + 1, h // (nh // nkv)].double()
+        p = torch.softmax((kk @ q[h].double()) * scale, dim=0)
+        out[h] = p @ vv
+    return out
+
+
+def _attn_tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(6, 3, 48, None), (4, 1, 16, 7), (8, 8, 256, 100),
+                                               (5, 5, 80, 64)])
+def test_attention_generic(dtype, nh, nkv, hd, window):
+    """Mixed batch: one sequence in prefill from 0, one continuing, one decoding."""
+    o = _ops(dtype)
+    lens = [70, 200, 131]
+    new = [70, 5, 1]            # tokens of this step; the rest is already cached
+    pc = Paged(lens, nkv, hd, dtype, 20 + hd)
+    T = sum(new)
+    q = _rand((T, nh * hd), dtype, 21)
+    token_seq = torch.tensor(sum([[b] * n for b, n in enumerate(new)], []), dtype=torch.int32, device=DEV)
+    token_pos = torch.tensor(sum([list(range(L - n, L)) for L, n in zip(lens, new)], []),
+                             dtype=torch.int32, device=DEV)
+    out = torch.empty((T, nh * hd), dtype=dtype, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    o.attn_generic(q, pc.k_pages, pc.v_pages, out, token_pos, token_seq, pc.seq_slot, pc.table,
+                   nh, nkv, hd, window, scale)
+    got = out.cpu().double().view(T, nh, hd)
+    qc = q.cpu().view(T, nh, hd)
+    for t in range(T):
+        b, pos = int(token_seq[t]), int(token_pos[t])
+        ref = attention_reference(qc[t], pc.k[b], pc.v[b], pos, window, scale)
+        assert torch.allclose(got[t], ref, **_attn_tol(dtype)), f"token {t} (seq {b}, pos {pos})"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("style", [0, 1])
+def test_rope_cache_write(dtype, style):
+    o = _ops(dtype)
+    nh, nkv, hd = 3, 2, 32
+    lens, new = [66, 9], [66, 2]
+    pc = Paged(lens, nkv, hd, dtype, 30, poison=False)
+    T = sum(new)
+    qkv = _rand((T, (nh + 2 * nkv) * hd), torch.float32, 31)
+    token_seq = torch.tensor(sum([[b] * n for b, n in enumerate(new)], []), dtype=torch.int32, device=DEV)
+    pos_list = sum([list(range(L - n, L)) for L, n in zip(lens, new)], [])
+    token_pos = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
+    half = hd // 2
+    inv = (1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64),
+                           torch.arange(half, dtype=torch.float64) / half)).float().to(DEV)
+    qo = torch.empty((T, nh * hd), dtype=dtype, device=DEV)
+    kp, vp = torch.zeros_like(pc.k_pages), torch.zeros_like(pc.v_pages)
+    o.rope_cache_write(qkv, qo, kp, vp, token_pos, token_seq, pc.seq_slot, pc.table, inv, style,
+                       nh, nkv, hd)
+    ang = torch.tensor(pos_list, dtype=torch.float32)[:, None] * inv.cpu()[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    x = qkv.cpu().view(T, nh + 2 * nkv, hd)
+    rot = x[:, :nh + nkv].clone()
+    if style == 0:
+        a, b = rot[..., :half].clone(), rot[..., half:].clone()
+        rot[..., :half], rot[..., half:] = a * c - b * s, a * s + b * c
+    else:
+        a, b = rot[..., 0::2].clone(), rot[..., 1::2].clone()
+        rot[..., 0::2], rot[..., 1::2] = a * c - b * s, a * s + b * c
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    assert torch.allclose(qo.cpu().float().view(T, nh, hd), rot[:, :nh], **tol)
+    table = pc.table.cpu()
+    for t in range(T):
+        b, pos = int(token_seq[t]), pos_list[t]
+        page = int(table[pc.slots[b], pos // PAGE])
+        assert torch.allclose(kp[page, :, pos % PAGE, :].cpu().float(), rot[t, nh:], **tol)
+        assert torch.allclose(vp[page, :, :, pos % PAGE].cpu().float(), x[t, nh + nkv:], **tol)
+    # nothing else was written
+    assert int((kp != 0).any(-1).sum()) <= T * nkv
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, None), (8, 2, 128, 100), (4, 4, 64, 33),
+                                               (12, 1, 32, None), (32, 8, 128, 4096), (10, 5, 64, 64)])
+def test_attention_decode_bf16(nh, nkv, hd, window):
+    """Split-KV decode kernel: lengths around the 32-key groups and page borders, and
+    every split count from one to more than there are groups."""
+    from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
+    from torchless_rs_b200.parts.runtime import Workspace
+    dtype = torch.bfloat16
+    att = AttentionBf16.get(hd)
+    lens = [1, 31, 32, 33, 64, 65, 127, 129, 300, 1000]
+    pc = Paged(lens, nkv, hd, dtype, 40 + hd)
+    B = len(lens)
+    q = _rand((B, nh * hd), dtype, 41)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    ws = Workspace(torch.device(DEV))
+    qc = q.cpu().view(B, nh, hd)
+    refs = [attention_reference(qc[b], pc.k[b], pc.v[b], lens[b] - 1, window, scale) for b in range(B)]
+    for n_splits in (1, 2, 3, 7, 40):
+        out = torch.full((B, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        att.decode(q, pc.k_pages, pc.v_pages, out, seq_len, pc.seq_slot, pc.table, nh, nkv, window,
+                   scale, n_splits, ws)
+        got = out.cpu().double().view(B, nh, hd)
+        for b in range(B):
+            assert torch.allclose(got[b], refs[b], **_attn_tol(dtype)), \
+                f"splits {n_splits} seq {b} (len {lens[b]})"
+
+
+def test_attention_decode_far_key_stands_out():
+    """Random keys give near-uniform weights, which would hide a key that is skipped
+    or read from the wrong page.  Here one far key matches the query strongly, so the
+    output must be that key's value; its place runs over group, page and window edges."""
+    from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
+    from torchless_rs_b200.parts.runtime import Workspace
+    nh, nkv, hd, n = 8, 2, 128, 700
+    dtype = torch.bfloat16
+    att = AttentionBf16.get(hd)
+    ws = Workspace(torch.device(DEV))
+    for window in (None, 300):
+        lo = 0 if window is None else n - window
+        for hot in (lo, lo + 1, lo + 31, lo + 32, 447, 448, 511, 512, n - 2, n - 1):
+            pc = Paged([n], nkv, hd, dtype, 50, poison=True)
+            q = _rand((1, nh * hd), dtype, 51)
+            qh = q.view(nh, hd).float()
+            # key `hot` of each kv head points along the mean query of its heads, times 4
+            k_dense = pc.k[0].clone()
+            for kvh in range(nkv):
+                qm = qh[kvh * (nh // nkv):(kvh + 1) * (nh // nkv)].mean(0).cpu()
+                k_dense[hot, kvh] = (qm * 4).to(dtype)
+            page = int(pc.table[pc.slots[0], hot // PAGE])
+            pc.k_pages[page, :, hot % PAGE, :] = k_dense[hot].to(DEV)
+            pc.k[0] = k_dense
+            seq_len = torch.tensor([n], dtype=torch.int32, device=DEV)
+            out = torch.empty((1, nh * hd), dtype=dtype, device=DEV)
+            scale = 1 / math.sqrt(hd)
+            att.decode(q, pc.k_pages, pc.v_pages, out, seq_len, pc.seq_slot, pc.table, nh, nkv,
+                       window, scale, 5, ws)
+            ref = attention_reference(q.cpu().view(nh, hd), pc.k[0], pc.v[0], n - 1, window, scale)
+            assert torch.allclose(out.cpu().double().view(nh, hd), ref, rtol=2e-2, atol=2e-2), \
+                f"window {window} hot key {hot}"

@@ -4,7 +4,8 @@ Two configurations of the architecture that differ in every size and option:
 layers 2/3, hidden 64/96, heads 4/3, key/value heads 2/1, head size 16/32,
 intermediate 176/256, vocabulary 256/384, theta 1e4/1e6, window 16/none, eps
 1e-5/1e-6; a third has a head size that is not hidden/heads and a vocabulary that
-is no multiple of 8."""
+is no multiple of 8; a fourth has a head size and window that the tensor-core
+attention kernels take."""
 from __future__ import annotations
 
 import os
@@ -34,7 +35,14 @@ TINY_C = {
     "rope_theta": 50000.0, "sliding_window": 70, "rms_norm_eps": 3e-6,
     "tie_word_embeddings": False, "max_position_embeddings": 4096,
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+TINY_D = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 320, "vocab_size": 512,
+    "rope_theta": 10000.0, "sliding_window": 40, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_model_dir(cfg: dict, seed: int, dtype=torch.bfloat16, where: str | None = None) -> str:

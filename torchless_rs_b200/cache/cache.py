@@ -9,7 +9,8 @@ advances (src/model/mod.rs:93).  Here many sequences live at once:
   back when the sequence ends, then used again;
 * layers whose mixers ask for the same thing form a *group* with storage of its own.
   A paged group holds keys and values in pages of `PAGE` positions,
-  [layers, 2, pages, kv_heads, PAGE, head_dim], and a table from (slot, position //
+  [layers, 2, pages, kv_heads, PAGE * head_dim] (keys as [PAGE, head_dim], values
+  transposed as [head_dim, PAGE]), and a table from (slot, position //
   PAGE) to a page.  A group with a window gives pages back as soon as every position
   in them has left the window of the sequence's next position;
 * a state group holds [layers, slots, *shape], zeroed when a slot is taken.
@@ -38,7 +39,7 @@ def pages_for(n_tokens: int) -> int:
 class PagedView:
     """What an attention mixer gets for its layer."""
     k_pages: torch.Tensor       # [pages, kv_heads, PAGE, head_dim]
-    v_pages: torch.Tensor
+    v_pages: torch.Tensor       # [pages, kv_heads, head_dim, PAGE]: values lie transposed
     page_table: torch.Tensor    # [slots, pages per sequence] int32, on the device
     window: Optional[int]
     group: "PagedGroup"
@@ -52,7 +53,7 @@ class PagedGroup:
         self.n_pages = n_pages
         self.pool = FreeList(n_pages, "cache page")
         self.storage = torch.zeros(
-            (len(self.layers), 2, n_pages, request.num_kv_heads, PAGE, request.head_dim),
+            (len(self.layers), 2, n_pages, request.num_kv_heads, PAGE * request.head_dim),
             dtype=dtype, device=device)
         self.table_host = np.full((max_slots, table_width), -1, dtype=np.int32)
         self.table_dev = torch.full((max_slots, table_width), -1, dtype=torch.int32, device=device)
@@ -115,8 +116,10 @@ class PagedGroup:
 
     def view(self, layer: int) -> PagedView:
         i = self.layers.index(layer)
-        return PagedView(self.storage[i, 0], self.storage[i, 1], self.table_dev,
-                         self.request.window, self)
+        r = self.request
+        k = self.storage[i, 0].view(self.n_pages, r.num_kv_heads, PAGE, r.head_dim)
+        v = self.storage[i, 1].view(self.n_pages, r.num_kv_heads, r.head_dim, PAGE)
+        return PagedView(k, v, self.table_dev, r.window, self)
 
 
 class StateGroup:

@@ -3,7 +3,31 @@ returns False for a case it does not take; the caller then uses the CUDA-core
 kernel."""
 from __future__ import annotations
 
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict
+
+import torch
+
+from . import build
+from .ops import KernelError, _check, _need, _ptr, _stream
+
+FAST_HEAD_DIMS = (32, 64, 128)
+MAX_GROUP = 16        # query heads per key/value head that one instruction's rows hold
+TARGET_BLOCKS = 592   # 148 SMs x 2 resident blocks x 2 waves
+
+for _hd in FAST_HEAD_DIMS:
+    build.register_library(f"attn_bf16_hd{_hd}", ("attention_decode_bf16.cu",),
+                           (f"-DHEAD_DIM={_hd}",))
+
+
+def decode_splits(batch_size: int, nkv: int, max_len: int, window) -> int:
+    """How many blocks share the keys of one (sequence, kv head)."""
+    span = min(max_len, window) if window else max_len
+    groups = (span + 31) // 32 + 1
+    by_work = max(1, (groups + 3) // 4)          # at least one 32-key group per warp
+    by_fill = max(1, TARGET_BLOCKS // max(1, batch_size * nkv))
+    return max(1, min(by_work, by_fill, 64))
 
 
 class AttentionBf16:
@@ -17,6 +41,37 @@ class AttentionBf16:
 
     def __init__(self, head_dim: int):
         self.head_dim = head_dim
+        self.lib = None
+        if head_dim in FAST_HEAD_DIMS:
+            self.lib = build.load_library(f"attn_bf16_hd{head_dim}")
+            self._decode = getattr(self.lib, f"tl_attn_decode_hd{head_dim}")
+            self._decode.restype = c_int
+            self._scratch = getattr(self.lib, f"tl_attn_decode_scratch_floats_hd{head_dim}")
+            self._scratch.restype = c_longlong
+
+    def decode(self, q, k_pages, v_pages, out, seq_len, seq_slot, page_table, nh, nkv, window,
+               scale, n_splits, workspace) -> None:
+        """One new token per sequence; `q` and `out` are [sequences, nh * head_dim]."""
+        if self.lib is None:
+            raise KernelError(f"no tensor-core decode attention for head size {self.head_dim}")
+        for t, n in ((q, "q"), (k_pages, "k pages"), (v_pages, "v pages"), (out, "out")):
+            _need(t, torch.bfloat16, f"attn decode {n}")
+        B = q.shape[0]
+        floats = self._scratch(c_int(B), c_int(nh), c_int(n_splits))
+        part = workspace.get("attn_decode_partials", (floats,), torch.float32)
+        _check(self._decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(part),
+                            _ptr(seq_len), _ptr(seq_slot), _ptr(page_table),
+                            c_int(page_table.stride(0)), c_int(B), c_int(nh), c_int(nkv),
+                            c_int(window or 0), c_float(scale), c_int(n_splits), _stream()),
+               "attn_decode")
 
     def run(self, q, cache_view, out, batch, nh, nkv, window, scale, workspace) -> bool:
+        if self.lib is None or nh // nkv > MAX_GROUP:
+            return False
+        if batch.is_decode:
+            n_splits = decode_splits(batch.n_seqs, nkv, batch.max_len, window)
+            self.decode(q, cache_view.k_pages, cache_view.v_pages, out, batch.seq_len,
+                        batch.seq_slot, cache_view.page_table, nh, nkv, window, scale, n_splits,
+                        workspace)
+            return True
         return False

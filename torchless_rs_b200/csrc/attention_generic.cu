@@ -92,11 +92,11 @@ attn_generic_kernel(const act_t* __restrict__ q, const act_t* __restrict__ k_pag
       const bool two = tid + ATT_THREADS < hd;
       for (int j = 0; j < cnt; ++j) {
         const int key = base + j;
-        const act_t* vrow =
-            v_pages + (size_t)pg[j] * page_elems + head_off + (size_t)(key % TL_PAGE) * hd;
+        // values lie transposed in a page: [hd][TL_PAGE]
+        const act_t* vcol = v_pages + (size_t)pg[j] * page_elems + head_off + (key % TL_PAGE);
         const float pj = ps[j];
-        acc0 = fmaf(pj, to_f32(vrow[tid]), acc0);
-        if (two) acc1 = fmaf(pj, to_f32(vrow[tid + ATT_THREADS]), acc1);
+        acc0 = fmaf(pj, to_f32(vcol[(size_t)tid * TL_PAGE]), acc0);
+        if (two) acc1 = fmaf(pj, to_f32(vcol[(size_t)(tid + ATT_THREADS) * TL_PAGE]), acc1);
       }
     }
     __syncthreads();  // ps and pg are rewritten by the next chunk

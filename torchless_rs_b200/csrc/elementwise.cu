@@ -65,7 +65,9 @@ extern "C" int TL_NAME(tl_rmsnorm)(const float* x, const int* rows, const void* 
 // write src/model/kv_cache.rs:87-104; v is not rotated).
 //   qkv      [T, ld] 32-bit: nh*hd columns of q, then nkv*hd of k, then nkv*hd of v
 //   q_out    [T, nh*hd]
-//   k_pages, v_pages  [n_pages, nkv, TL_PAGE, hd]; null when the layer keeps no cache
+//   k_pages  [n_pages, nkv, TL_PAGE, hd]; v_pages  [n_pages, nkv, hd, TL_PAGE] (values are
+//            kept transposed, so that the attention kernels read runs of positions of
+//            one dimension); both null when the layer keeps no cache
 //   inv_freq [hd/2] 32-bit, null for no rotation
 //   style 0: dimension i pairs with i + hd/2;  style 1: 2i pairs with 2i+1
 // The angle pos * inv_freq and its sine and cosine are computed in 32-bit.
@@ -84,13 +86,14 @@ __global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
   const int half = hd >> 1;
   const float* row = qkv + (size_t)t * ld;
   const bool has_kv = k_pages != nullptr;
-  size_t page_base = 0;
+  size_t page_base = 0, vpage_base = 0;
   bool page_ok = false;
   if (has_kv) {
     const int slot = seq_slot[token_seq[t]];
     const int page = page_table[(size_t)slot * table_stride + pos / TL_PAGE];
     page_ok = page >= 0;
-    page_base = (size_t)(page_ok ? page : 0) * nkv * TL_PAGE * hd + (size_t)(pos % TL_PAGE) * hd;
+    vpage_base = (size_t)(page_ok ? page : 0) * nkv * TL_PAGE * hd;
+    page_base = vpage_base + (size_t)(pos % TL_PAGE) * hd;
   }
   const int n_rot_heads = nh + (has_kv ? nkv : 0);
   const float fpos = (float)pos;
@@ -120,7 +123,8 @@ __global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
     const float* vrow = row + (size_t)(nh + nkv) * hd;
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
       const int h = idx / hd, d = idx - h * hd;
-      v_pages[page_base + (size_t)h * TL_PAGE * hd + d] = from_f32<act_t>(vrow[idx]);
+      v_pages[vpage_base + (size_t)h * TL_PAGE * hd + (size_t)d * TL_PAGE + (pos % TL_PAGE)] =
+          from_f32<act_t>(vrow[idx]);
     }
   }
 }
