@@ -19,6 +19,10 @@ TARGET_BLOCKS = 592   # 148 SMs x 2 resident blocks x 2 waves
 for _hd in FAST_HEAD_DIMS:
     build.register_library(f"attn_bf16_hd{_hd}", ("attention_decode_bf16.cu",),
                            (f"-DHEAD_DIM={_hd}",))
+    # the same kernels with a fixed scratch array inside the library, for callers that must
+    # not allocate (see attention_decode_noalloc.h); nothing in this package loads it
+    build.register_library(f"attn_noalloc_bf16_hd{_hd}", ("attention_decode_noalloc.cu",),
+                           (f"-DHEAD_DIM={_hd}",))
 
 
 def decode_splits(batch_size: int, nkv: int, max_len: int, window) -> int:

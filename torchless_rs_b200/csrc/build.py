@@ -13,6 +13,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -53,13 +54,26 @@ def find_nvcc() -> str:
                      "kernels of this package cannot be built and there is no other path")
 
 
-def _headers() -> List[str]:
-    return sorted(f for f in os.listdir(_HERE) if f.endswith((".cuh", ".h")))
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _closure(sources: Sequence[str]) -> List[str]:
+    """The sources and every file of this folder that they include, directly or not."""
+    seen: List[str] = []
+    todo = list(sources)
+    while todo:
+        f = todo.pop()
+        if f in seen or not os.path.isfile(os.path.join(_HERE, f)):
+            continue
+        seen.append(f)
+        with open(os.path.join(_HERE, f), "r", encoding="utf-8") as fh:
+            todo.extend(_INCLUDE.findall(fh.read()))
+    return sorted(seen)
 
 
 def _digest(sources: Sequence[str], defines: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for f in list(sources) + _headers():
+    for f in _closure(sources):
         with open(os.path.join(_HERE, f), "rb") as fh:
             h.update(f.encode() + b"\0" + fh.read())
     h.update(" ".join(list(ARCH_FLAGS) + BASE_FLAGS + list(defines)).encode())
