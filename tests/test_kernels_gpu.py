@@ -279,3 +279,38 @@ def test_attention_decode_far_key_stands_out():
             ref = attention_reference(q.cpu().view(nh, hd), pc.k[0], pc.v[0], n - 1, window, scale)
             assert torch.allclose(out.cpu().double().view(nh, hd), ref, rtol=2e-2, atol=2e-2), \
                 f"window {window} hot key {hot}"
+
+
+# ---------------------------------------------------------------------------
+# tensor-core matrix products (tcgen05): every mode, every token tile, K splits, tails
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 4096, 4096), (16, 200, 72), (17, 384, 1000),
+                                   (33, 130, 64), (64, 6144, 512), (100, 256, 176), (129, 128, 192),
+                                   (300, 520, 328), (2048, 512, 256)])
+def test_gemm_tensor_core(M, N, K):
+    from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16
+    g = GemmBf16.get()
+    dtype = torch.bfloat16
+    a = _rand((M, K), dtype, 80)
+    w = _rand((2 * N, K), dtype, 81, 1.0 / math.sqrt(K))
+    ad, wd = a.double(), w.double()
+    ref = ad @ wd[:N].T
+    up = ad @ wd[N:].T
+    c = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    assert g.run(a, w[:N], c, 0)
+    assert torch.allclose(c.double(), ref, rtol=1e-4, atol=1e-4), f"store: {(c.double()-ref).abs().max()}"
+    base = _rand((M, N), torch.float32, 82)
+    c2 = base.clone()
+    assert g.run(a, w[:N], c2, 1)
+    assert torch.allclose(c2.double(), base.double() + ref, rtol=1e-4, atol=1e-4)
+    c3 = torch.empty((M, N), dtype=dtype, device=DEV)
+    assert g.run(a, w[:N], c3, 3)
+    assert torch.allclose(c3.double(), ref, rtol=1e-2, atol=1e-2)
+    c4 = torch.empty((M, N), dtype=dtype, device=DEV)
+    assert g.run(a, w, c4, 2)
+    assert torch.allclose(c4.double(), ref / (1 + torch.exp(-ref)) * up, rtol=1e-2, atol=1e-2)
+    # a second run gives the same bits (K splits are added in a fixed order)
+    c5 = torch.empty_like(c)
+    assert g.run(a, w[:N], c5, 0)
+    assert torch.equal(c, c5)
+    assert g.take_error() == 0

@@ -1,8 +1,15 @@
-"""Tensor-core matrix products of the bfloat16 path.  `run` returns False for a
-shape it does not take; the caller then uses the CUDA-core kernel."""
+"""Tensor-core matrix products of the bfloat16 path (kernels in gemm_tc.cu).  `run`
+returns False for a shape it does not take; the caller then uses the CUDA-core kernel."""
 from __future__ import annotations
 
+from ctypes import c_int, c_longlong, c_void_p
+
 import torch
+
+from . import build
+from .ops import KernelError, _check, _ptr, _stream
+
+build.register_library("gemm_tc", ("gemm_tc.cu",), ())
 
 
 class GemmBf16:
@@ -14,5 +21,45 @@ class GemmBf16:
             cls._inst = cls()
         return cls._inst
 
+    def __init__(self):
+        self.lib = build.load_library("gemm_tc")
+        self.lib.tl_gemm_tc.restype = c_int
+        self.lib.tl_gemm_tc_ws_floats.restype = c_longlong
+        self.lib.tl_gemm_tc_counters.restype = c_int
+        self.lib.tl_gemm_tc_take_error.restype = c_int
+        self._scratch = {}
+
+    def _scratch_for(self, device: torch.device):
+        key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+        if key not in self._scratch:
+            ws = torch.empty(self.lib.tl_gemm_tc_ws_floats(), dtype=torch.float32, device=device)
+            counters = torch.zeros(self.lib.tl_gemm_tc_counters(), dtype=torch.int32, device=device)
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            self._scratch[key] = (ws, counters, sms)
+        return self._scratch[key]
+
     def run(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> bool:
-        return False
+        """out (op)= a @ w.T.  Shapes and types are checked by the caller's generic path
+        when this returns False."""
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            return False
+        if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            return False
+        M, K = a.shape
+        N = out.shape[1]
+        want = torch.float32 if mode in (0, 1) else torch.bfloat16
+        if out.dtype != want or w.shape != ((2 * N if mode == 2 else N), K) or out.shape[0] != M:
+            raise KernelError(f"gemm: shapes or types do not fit: a {tuple(a.shape)} w {tuple(w.shape)} "
+                              f"out {tuple(out.shape)} {out.dtype} mode {mode}")
+        ws, counters, sms = self._scratch_for(a.device)
+        st = self.lib.tl_gemm_tc(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
+                                 c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(mode),
+                                 _ptr(ws), _ptr(counters), c_int(sms), _stream())
+        if st == -2:
+            return False
+        _check(st, "gemm_tc")
+        return True
+
+    def take_error(self) -> int:
+        """Nonzero if a kernel gave up on a bounded wait since the last call (synchronises)."""
+        return int(self.lib.tl_gemm_tc_take_error())

@@ -1,0 +1,441 @@
+// Matrix products of the bfloat16 path on the fifth-generation tensor cores.
+//
+//   C[M, N] (op)= X[M, K] * W[N, K]^T      X, W bfloat16 with K contiguous, 32-bit sums
+//
+// The product is computed transposed: 128 rows of W are the M operand of tcgen05.mma,
+// a tile of BN rows of X (tokens) is its N operand, and the accumulator lies in tensor
+// memory as [128 weight rows][BN tokens].  So the same kernel serves one decoded token
+// per sequence (BN = 16: the weights stream through TMA at full width and the padding
+// costs nothing that matters) and prefill (BN = 256).  Operands come by TMA into
+// 128-byte-swizzled shared memory tiles of 64 K-elements; one thread issues the
+// instructions; four warps read the accumulator back with tcgen05.ld and write C, each
+// warp-store covering 32 consecutive columns of one row of C.
+//
+// When a product has too few tiles to fill the GPU (decode), K is split over
+// blockIdx.z.  Every split writes its partial tile to scratch memory; the block that
+// arrives last at the tile's counter adds the partials in split order and writes C, so
+// the result does not depend on which block came last.
+//
+// Output modes as in gemm_generic.cu: 0 store 32-bit, 1 add into 32-bit C, 2 SiLU-gate
+// (W holds N gate rows then N up rows; two accumulators), 3 store bfloat16.
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code
+// in tl_gemm_tc_error, stops waiting everywhere, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#define TILE_N 128        // weight rows per tile (M of the instruction)
+#define TILE_K 64         // K elements per shared memory tile (128 bytes)
+#define UMMA_K 16
+#define NUM_THREADS 192   // warps 0-3 epilogue, warp 4 TMA, warp 5 MMA
+#define WAIT_LIMIT (1u << 22)
+
+#define MODE_STORE_F32 0
+#define MODE_ACCUM_F32 1
+#define MODE_SWIGLU 2
+#define MODE_STORE_ACT 3
+
+__device__ int tl_gemm_tc_error = 0;
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the bound is hit or another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = code;
+  atomicCAS(&tl_gemm_tc_error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(slot)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier gets one arrival when all tcgen05.mma issued so far by this thread are done.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
+      "%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared memory matrix descriptor of a K-major tile whose rows are 128 bytes with the
+// 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                     // leading byte offset (unused with a swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                     // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+// ---------------------------------------------------------------------------
+// The kernel.  grid = (tiles of 128 weight rows, tiles of BN tokens, K splits).
+// ---------------------------------------------------------------------------
+struct GemmArgs {
+  void* C;
+  float* ws;        // partial tiles of the K splits
+  int* counters;    // one per output tile, zero between launches
+  int ldc, M, N, K, mode, kb_per_split, stages;
+};
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+               const GemmArgs args) {
+  constexpr uint32_t A_BYTES = TILE_N * TILE_K * 2;
+  constexpr uint32_t B_BYTES = BN * TILE_K * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
+  constexpr uint32_t ACC_COLS = BN * (SWIGLU ? 2 : 1);
+  constexpr uint32_t TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;   // a power of two >= 32
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(TILE_N >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stages = args.stages;
+  uint64_t* full_bar = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + 8;
+  uint64_t* acc_bar = empty_bar + 8;
+  uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* last_flag = (int*)(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * TILE_N, m0 = blockIdx.y * BN;
+  const int splits = gridDim.z, split = blockIdx.z;
+  const int kb_total = (args.K + TILE_K - 1) / TILE_K;
+  const int kb0 = split * args.kb_per_split;
+  const int kb1 = min(kb0 + args.kb_per_split, kb_total);
+  const int n_kb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4 && lane == 0) {
+    // ---- TMA producer
+    for (int i = 0; i < n_kb; ++i) {
+      const int s = i % stages;
+      const uint32_t ph = (uint32_t)(i / stages) & 1u;
+      if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) break;
+      uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      const int k = (kb0 + i) * TILE_K;
+      tma_load_2d(st, &tm_w, &full_bar[s], k, n0);
+      if (SWIGLU) tma_load_2d(st + A_BYTES, &tm_w, &full_bar[s], k, args.N + n0);
+      tma_load_2d(st + A_BYTES * (SWIGLU ? 2 : 1), &tm_x, &full_bar[s], k, m0);
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ---- MMA issuer
+    bool ok = true;
+    for (int i = 0; i < n_kb && ok; ++i) {
+      const int s = i % stages;
+      const uint32_t ph = (uint32_t)(i / stages) & 1u;
+      ok = mbar_wait(&full_bar[s], ph, abort_flag, 2);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+      const uint64_t da = smem_desc_k128(sa);
+      const uint64_t da2 = smem_desc_k128(sa + A_BYTES);
+      const uint64_t db = smem_desc_k128(sa + A_BYTES * (SWIGLU ? 2 : 1));
+#pragma unroll
+      for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+        const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+        const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);   // 32 bytes per step
+        umma_bf16(tmem_base, da + adv, db + adv, IDESC, acc);
+        if (SWIGLU) umma_bf16(tmem_base + BN, da2 + adv, db + adv, IDESC, acc);
+      }
+      umma_commit(&empty_bar[s]);   // the stage is free once these instructions have read it
+    }
+    if (ok) umma_commit(acc_bar);
+  } else if (warp < 4) {
+    // ---- epilogue: thread = one weight row = one column of C
+    const bool ok = mbar_wait(acc_bar, 0, abort_flag, 3);
+    tc_fence_after();
+    const int row = warp * 32 + lane;
+    const int n = n0 + row;
+    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    const size_t tile_floats = (size_t)BN * TILE_N * (SWIGLU ? 2 : 1);
+    float* wsp = splits > 1 ? args.ws + ((size_t)tile_id * splits + split) * tile_floats : nullptr;
+    if (ok) {
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16], u[16];
+        tmem_ld16(taddr + c0, r);
+        if (SWIGLU) tmem_ld16(taddr + BN + c0, u);
+        tmem_ld_wait();
+        if (splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            wsp[(size_t)(c0 + j) * TILE_N + row] = __uint_as_float(r[j]);
+            if (SWIGLU) wsp[(size_t)(BN + c0 + j) * TILE_N + row] = __uint_as_float(u[j]);
+          }
+        } else if (n < args.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c0 + j;
+            if (m >= args.M) break;
+            const float v = __uint_as_float(r[j]);
+            const size_t idx = (size_t)m * args.ldc + n;
+            if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(v) * __uint_as_float(u[j]));
+            else if (args.mode == MODE_STORE_F32) ((float*)args.C)[idx] = v;
+            else if (args.mode == MODE_ACCUM_F32) ((float*)args.C)[idx] += v;
+            else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+    if (splits > 1 && ok) {
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 0) *last_flag = (atomicAdd(&args.counters[tile_id], 1) == splits - 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag) {
+        __threadfence();
+        const float* base = args.ws + (size_t)tile_id * splits * tile_floats;
+        if (n < args.N) {
+          for (int c = 0; c < BN; ++c) {
+            const int m = m0 + c;
+            if (m >= args.M) break;
+            float v = 0.0f, uu = 0.0f;
+            for (int s = 0; s < splits; ++s) {
+              v += __ldcg(base + (size_t)s * tile_floats + (size_t)c * TILE_N + row);
+              if (SWIGLU) uu += __ldcg(base + (size_t)s * tile_floats + (size_t)(BN + c) * TILE_N + row);
+            }
+            const size_t idx = (size_t)m * args.ldc + n;
+            if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(v) * uu);
+            else if (args.mode == MODE_STORE_F32) ((float*)args.C)[idx] = v;
+            else if (args.mode == MODE_ACCUM_F32) ((float*)args.C)[idx] += v;
+            else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(v);
+          }
+        }
+        if (threadIdx.x == 0) args.counters[tile_id] = 0;   // ready for the next launch
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor maps (cached), tile and split choice, launch.
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// [rows, K] bfloat16, row stride ld elements; boxes of 64 K-elements x box_rows rows.
+static bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld,
+                     int box_rows) {
+  typedef std::tuple<const void*, long long, long long, long long, int> Key;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key(ptr, rows, K, ld, box_rows);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *map = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = m;
+  *map = m;
+  return true;
+}
+
+template <int BN, bool SWIGLU>
+static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int splits,
+                  size_t smem_budget, cudaStream_t stream) {
+  const size_t stage = (size_t)TILE_N * TILE_K * 2 * (SWIGLU ? 2 : 1) + (size_t)BN * TILE_K * 2;
+  int stages = (int)((smem_budget - 1024 - 256) / stage);
+  stages = stages > 8 ? 8 : stages;
+  if (stages < 2) return -2;
+  a.stages = stages;
+  const size_t smem = 1024 + stages * stage + 256;
+  static size_t configured = 0;   // per instantiation
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWIGLU>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  dim3 grid((a.N + TILE_N - 1) / TILE_N, (a.M + BN - 1) / BN, splits);
+  gemm_tc_kernel<BN, SWIGLU><<<grid, NUM_THREADS, smem, stream>>>(tw, tx, a);
+  return (int)cudaGetLastError();
+}
+
+// Scratch the launcher may use: floats for partial tiles and ints for tile counters
+// (the counters must be zero before the first launch; the kernel leaves them zero).
+extern "C" long long tl_gemm_tc_ws_floats() { return 8ll * 1024 * 1024; }
+extern "C" int tl_gemm_tc_counters() { return 4096; }
+
+// Returns 0, a CUDA error, or -2 when these sizes or alignments are not taken (the
+// caller then uses the CUDA-core kernel).  N counts output columns; in mode 2 W has 2N rows.
+extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* C, int ldc, int M,
+                          int N, int K, int mode, float* ws, int* counters, int num_sms,
+                          cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+    return -2;
+  if (mode < 0 || mode > 3) return -1;
+  const bool swiglu = mode == MODE_SWIGLU;
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (swiglu && bn == 256 && false) return -2;
+  const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = (M + bn - 1) / bn;
+  const long long tiles = (long long)n_tiles * m_tiles;
+  const int kb_total = (K + TILE_K - 1) / TILE_K;
+  // two blocks per SM fit while the token tile is small
+  const bool two_per_sm = bn <= 64;
+  const size_t budget = two_per_sm ? 112 * 1024 : 224 * 1024;
+  const long long slots = (long long)num_sms * (two_per_sm ? 2 : 1);
+  int splits = 1;
+  if (tiles < slots && ws && counters && tiles <= tl_gemm_tc_counters()) {
+    splits = (int)(slots / tiles);
+    if (splits > kb_total / 2) splits = kb_total / 2;
+    const long long per_tile = (long long)bn * TILE_N * (swiglu ? 2 : 1);
+    while (splits > 1 && tiles * splits * per_tile > tl_gemm_tc_ws_floats()) --splits;
+    if (splits < 1) splits = 1;
+  }
+  int kb_per_split = (kb_total + splits - 1) / splits;
+  splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
+  CUtensorMap tw, tx;
+  if (!make_map(&tw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, TILE_N)) return -2;
+  if (!make_map(&tx, X, M, K, ldx, bn)) return -2;
+  GemmArgs a;
+  a.C = C; a.ws = ws; a.counters = counters; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
+  a.mode = mode; a.kb_per_split = kb_per_split; a.stages = 0;
+#define DISPATCH(BN_)                                                                      \
+  return swiglu ? launch<BN_, true>(tw, tx, a, splits, budget, stream)                    \
+                : launch<BN_, false>(tw, tx, a, splits, budget, stream)
+  switch (bn) {
+    case 16: DISPATCH(16);
+    case 32: DISPATCH(32);
+    case 64: DISPATCH(64);
+    case 128: DISPATCH(128);
+    default: DISPATCH(256);
+  }
+#undef DISPATCH
+}
+
+// Reads and clears the error word that a kernel sets when one of its bounded waits ran
+// out (0 = none; 1 producer, 2 issuer, 3 epilogue).  Synchronises the device.
+extern "C" int tl_gemm_tc_take_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, tl_gemm_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(tl_gemm_tc_error, &zero, sizeof(int));
+  return v;
+}
