@@ -73,7 +73,7 @@ class AttentionBf16:
         if self.lib is None or nh // nkv > MAX_GROUP:
             return False
         if batch.is_decode:
-            n_splits = decode_splits(batch.n_seqs, nkv, batch.max_len, window)
+            n_splits = decode_splits(batch.n_seqs, nkv, batch.len_bucket, window)
             self.decode(q, cache_view.k_pages, cache_view.v_pages, out, batch.seq_len,
                         batch.seq_slot, cache_view.page_table, nh, nkv, window, scale, n_splits,
                         workspace)

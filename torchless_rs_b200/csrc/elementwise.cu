@@ -81,51 +81,43 @@ __global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
                                         const int* __restrict__ page_table, int table_stride,
                                         const float* __restrict__ inv_freq, int style, int nh,
                                         int nkv, int hd) {
-  const int t = blockIdx.x;
+  // grid (tokens, heads): query heads, then key heads, then value heads
+  const int t = blockIdx.x, h = blockIdx.y;
   const int pos = token_pos[t];
   const int half = hd >> 1;
-  const float* row = qkv + (size_t)t * ld;
-  const bool has_kv = k_pages != nullptr;
-  size_t page_base = 0, vpage_base = 0;
-  bool page_ok = false;
-  if (has_kv) {
+  const float* row = qkv + (size_t)t * ld + (size_t)h * hd;
+  size_t page_base = 0;
+  bool page_ok = true;
+  if (h >= nh) {
     const int slot = seq_slot[token_seq[t]];
     const int page = page_table[(size_t)slot * table_stride + pos / TL_PAGE];
     page_ok = page >= 0;
-    vpage_base = (size_t)(page_ok ? page : 0) * nkv * TL_PAGE * hd;
-    page_base = vpage_base + (size_t)(pos % TL_PAGE) * hd;
+    const int kvh = h - nh < nkv ? h - nh : h - nh - nkv;
+    page_base = ((size_t)(page_ok ? page : 0) * nkv + kvh) * (size_t)(TL_PAGE * hd);
   }
-  const int n_rot_heads = nh + (has_kv ? nkv : 0);
-  const float fpos = (float)pos;
-  for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
-    const int d0 = style == 0 ? i : 2 * i;
-    const int d1 = style == 0 ? i + half : 2 * i + 1;
-    const float a = row[h * hd + d0], b = row[h * hd + d1];
-    float ra = a, rb = b;
-    if (inv_freq) {
-      float s, c;
-      sincosf(fpos * inv_freq[i], &s, &c);
-      ra = a * c - b * s;
-      rb = a * s + b * c;
-    }
-    if (h < nh) {
-      act_t* dst = q_out + (size_t)t * nh * hd + h * hd;
-      dst[d0] = from_f32<act_t>(ra);
-      dst[d1] = from_f32<act_t>(rb);
-    } else if (page_ok) {
-      act_t* dst = k_pages + page_base + (size_t)(h - nh) * TL_PAGE * hd;
+  if (!page_ok) return;
+  if (h < nh + nkv) {
+    act_t* dst = h < nh ? q_out + (size_t)t * nh * hd + (size_t)h * hd
+                        : k_pages + page_base + (size_t)(pos % TL_PAGE) * hd;
+    const float fpos = (float)pos;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const int d0 = style == 0 ? i : 2 * i;
+      const int d1 = style == 0 ? i + half : 2 * i + 1;
+      const float a = row[d0], b = row[d1];
+      float ra = a, rb = b;
+      if (inv_freq) {
+        float s, c;
+        sincosf(fpos * inv_freq[i], &s, &c);
+        ra = a * c - b * s;
+        rb = a * s + b * c;
+      }
       dst[d0] = from_f32<act_t>(ra);
       dst[d1] = from_f32<act_t>(rb);
     }
-  }
-  if (has_kv && page_ok) {
-    const float* vrow = row + (size_t)(nh + nkv) * hd;
-    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-      const int h = idx / hd, d = idx - h * hd;
-      v_pages[vpage_base + (size_t)h * TL_PAGE * hd + (size_t)d * TL_PAGE + (pos % TL_PAGE)] =
-          from_f32<act_t>(vrow[idx]);
-    }
+  } else {
+    // values lie transposed in a page: [hd][TL_PAGE]
+    act_t* dst = v_pages + page_base + (pos % TL_PAGE);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[(size_t)d * TL_PAGE] = from_f32<act_t>(row[d]);
   }
 }
 
@@ -137,10 +129,13 @@ extern "C" int TL_NAME(tl_rope_cache_write)(const float* qkv, int ld, void* q_ou
                                             int nkv, int hd, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd & 1) return TL_ERR_BAD_ARG;
-  rope_cache_write_kernel<<<T, 128, 0, stream>>>(qkv, ld, (act_t*)q_out, (act_t*)k_pages,
-                                                 (act_t*)v_pages, token_pos, token_seq, seq_slot,
-                                                 page_table, table_stride, inv_freq, style, nh,
-                                                 nkv, hd);
+  const int heads = nh + (k_pages ? 2 * nkv : 0);
+  if (heads > 65535) return TL_ERR_UNSUPPORTED;
+  dim3 grid(T, heads);
+  rope_cache_write_kernel<<<grid, 64, 0, stream>>>(qkv, ld, (act_t*)q_out, (act_t*)k_pages,
+                                                   (act_t*)v_pages, token_pos, token_seq, seq_slot,
+                                                   page_table, table_stride, inv_freq, style, nh,
+                                                   nkv, hd);
   return TL_LAUNCH_STATUS();
 }
 

@@ -24,18 +24,13 @@ class GemmBf16:
     def __init__(self):
         self.lib = build.load_library("gemm_tc")
         self.lib.tl_gemm_tc.restype = c_int
-        self.lib.tl_gemm_tc_ws_floats.restype = c_longlong
-        self.lib.tl_gemm_tc_counters.restype = c_int
         self.lib.tl_gemm_tc_take_error.restype = c_int
         self._scratch = {}
 
     def _scratch_for(self, device: torch.device):
         key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
         if key not in self._scratch:
-            ws = torch.empty(self.lib.tl_gemm_tc_ws_floats(), dtype=torch.float32, device=device)
-            counters = torch.zeros(self.lib.tl_gemm_tc_counters(), dtype=torch.int32, device=device)
-            sms = torch.cuda.get_device_properties(device).multi_processor_count
-            self._scratch[key] = (ws, counters, sms)
+            self._scratch[key] = torch.cuda.get_device_properties(device).multi_processor_count
         return self._scratch[key]
 
     def run(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> bool:
@@ -51,10 +46,10 @@ class GemmBf16:
         if out.dtype != want or w.shape != ((2 * N if mode == 2 else N), K) or out.shape[0] != M:
             raise KernelError(f"gemm: shapes or types do not fit: a {tuple(a.shape)} w {tuple(w.shape)} "
                               f"out {tuple(out.shape)} {out.dtype} mode {mode}")
-        ws, counters, sms = self._scratch_for(a.device)
+        sms = self._scratch_for(a.device)
         st = self.lib.tl_gemm_tc(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
                                  c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(mode),
-                                 _ptr(ws), _ptr(counters), c_int(sms), _stream())
+                                 c_int(sms), _stream())
         if st == -2:
             return False
         _check(st, "gemm_tc")

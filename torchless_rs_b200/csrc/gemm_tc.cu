@@ -12,9 +12,11 @@
 // warp-store covering 32 consecutive columns of one row of C.
 //
 // When a product has too few tiles to fill the GPU (decode), K is split over
-// blockIdx.z.  Every split writes its partial tile to scratch memory; the block that
-// arrives last at the tile's counter adds the partials in split order and writes C, so
-// the result does not depend on which block came last.
+// blockIdx.z and the blocks of one tile form a thread-block cluster.  Each block puts
+// its partial tile into its own shared memory; after a cluster barrier the blocks share
+// the columns of the tile among them, and each adds the partials of its columns in split
+// order through distributed shared memory and writes C.  No scratch in global memory,
+// no atomics, the same bits every run.
 //
 // Output modes as in gemm_generic.cu: 0 store 32-bit, 1 add into 32-bit C, 2 SiLU-gate
 // (W holds N gate rows then N up rows; two accumulators), 3 store bfloat16.
@@ -148,6 +150,22 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
   return d;
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float ld_remote_f32(uint32_t local_saddr, uint32_t rank) {
+  uint32_t raddr;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_saddr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
 // ---------------------------------------------------------------------------
@@ -155,8 +173,6 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g));
 // ---------------------------------------------------------------------------
 struct GemmArgs {
   void* C;
-  float* ws;        // partial tiles of the K splits
-  int* counters;    // one per output tile, zero between launches
   int ldc, M, N, K, mode, kb_per_split, stages;
 };
 
@@ -246,9 +262,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const int row = warp * 32 + lane;
     const int n = n0 + row;
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-    const size_t tile_floats = (size_t)BN * TILE_N * (SWIGLU ? 2 : 1);
-    float* wsp = splits > 1 ? args.ws + ((size_t)tile_id * splits + split) * tile_floats : nullptr;
+    float* red = (float*)smem;   // partial tile [columns][128 rows]; the stages are free by now
     if (ok) {
       for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t r[16], u[16];
@@ -258,8 +272,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (splits > 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            wsp[(size_t)(c0 + j) * TILE_N + row] = __uint_as_float(r[j]);
-            if (SWIGLU) wsp[(size_t)(BN + c0 + j) * TILE_N + row] = __uint_as_float(u[j]);
+            red[(c0 + j) * TILE_N + row] = __uint_as_float(r[j]);
+            if (SWIGLU) red[(BN + c0 + j) * TILE_N + row] = __uint_as_float(u[j]);
           }
         } else if (n < args.N) {
 #pragma unroll
@@ -276,33 +290,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
       }
     }
-    if (splits > 1 && ok) {
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 0) *last_flag = (atomicAdd(&args.counters[tile_id], 1) == splits - 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*last_flag) {
-        __threadfence();
-        const float* base = args.ws + (size_t)tile_id * splits * tile_floats;
-        if (n < args.N) {
-          for (int c = 0; c < BN; ++c) {
-            const int m = m0 + c;
-            if (m >= args.M) break;
-            float v = 0.0f, uu = 0.0f;
-            for (int s = 0; s < splits; ++s) {
-              v += __ldcg(base + (size_t)s * tile_floats + (size_t)c * TILE_N + row);
-              if (SWIGLU) uu += __ldcg(base + (size_t)s * tile_floats + (size_t)(BN + c) * TILE_N + row);
-            }
-            const size_t idx = (size_t)m * args.ldc + n;
-            if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(v) * uu);
-            else if (args.mode == MODE_STORE_F32) ((float*)args.C)[idx] = v;
-            else if (args.mode == MODE_ACCUM_F32) ((float*)args.C)[idx] += v;
-            else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(v);
+  }
+  __syncwarp();
+  if (splits > 1) {
+    cluster_sync_all();   // every block's partial tile is in its shared memory
+    if (warp < 4) {
+      const int row = warp * 32 + lane;
+      const int n = n0 + row;
+      const uint32_t red_s = smem_u32(smem);
+      const int cols = min(BN, args.M - m0);
+      if (n < args.N && !*abort_flag) {
+        for (int c = (int)cluster_rank(); c < cols; c += splits) {
+          float v = 0.0f, uu = 0.0f;
+          for (int sp = 0; sp < splits; ++sp) {
+            v += ld_remote_f32(red_s + (uint32_t)(c * TILE_N + row) * 4u, (uint32_t)sp);
+            if (SWIGLU) uu += ld_remote_f32(red_s + (uint32_t)((BN + c) * TILE_N + row) * 4u, (uint32_t)sp);
           }
+          const size_t idx = (size_t)(m0 + c) * args.ldc + n;
+          if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(v) * uu);
+          else if (args.mode == MODE_STORE_F32) ((float*)args.C)[idx] = v;
+          else if (args.mode == MODE_ACCUM_F32) ((float*)args.C)[idx] += v;
+          else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(v);
         }
-        if (threadIdx.x == 0) args.counters[tile_id] = 0;   // ready for the next launch
       }
     }
+    cluster_sync_all();   // nobody leaves while others still read its shared memory
   }
   tc_fence_before();
   __syncthreads();
@@ -373,28 +385,34 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int 
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  dim3 grid((a.N + TILE_N - 1) / TILE_N, (a.M + BN - 1) / BN, splits);
-  gemm_tc_kernel<BN, SWIGLU><<<grid, NUM_THREADS, smem, stream>>>(tw, tx, a);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.N + TILE_N - 1) / TILE_N, (a.M + BN - 1) / BN, splits);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;   // the splits of one tile share their partials
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWIGLU>, tw, tx, a);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
-// Scratch the launcher may use: floats for partial tiles and ints for tile counters
-// (the counters must be zero before the first launch; the kernel leaves them zero).
-extern "C" long long tl_gemm_tc_ws_floats() { return 8ll * 1024 * 1024; }
-extern "C" int tl_gemm_tc_counters() { return 4096; }
+#define MAX_SPLITS 8   // portable cluster size
 
 // Returns 0, a CUDA error, or -2 when these sizes or alignments are not taken (the
 // caller then uses the CUDA-core kernel).  N counts output columns; in mode 2 W has 2N rows.
 extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* C, int ldc, int M,
-                          int N, int K, int mode, float* ws, int* counters, int num_sms,
-                          cudaStream_t stream) {
+                          int N, int K, int mode, int num_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
     return -2;
   if (mode < 0 || mode > 3) return -1;
   const bool swiglu = mode == MODE_SWIGLU;
   const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  if (swiglu && bn == 256 && false) return -2;
   const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = (M + bn - 1) / bn;
   const long long tiles = (long long)n_tiles * m_tiles;
   const int kb_total = (K + TILE_K - 1) / TILE_K;
@@ -403,11 +421,10 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   const size_t budget = two_per_sm ? 112 * 1024 : 224 * 1024;
   const long long slots = (long long)num_sms * (two_per_sm ? 2 : 1);
   int splits = 1;
-  if (tiles < slots && ws && counters && tiles <= tl_gemm_tc_counters()) {
+  if (tiles < slots && two_per_sm) {
     splits = (int)(slots / tiles);
     if (splits > kb_total / 2) splits = kb_total / 2;
-    const long long per_tile = (long long)bn * TILE_N * (swiglu ? 2 : 1);
-    while (splits > 1 && tiles * splits * per_tile > tl_gemm_tc_ws_floats()) --splits;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
     if (splits < 1) splits = 1;
   }
   int kb_per_split = (kb_total + splits - 1) / splits;
@@ -416,7 +433,7 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   if (!make_map(&tw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, TILE_N)) return -2;
   if (!make_map(&tx, X, M, K, ldx, bn)) return -2;
   GemmArgs a;
-  a.C = C; a.ws = ws; a.counters = counters; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
+  a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
   a.mode = mode; a.kb_per_split = kb_per_split; a.stages = 0;
 #define DISPATCH(BN_)                                                                      \
   return swiglu ? launch<BN_, true>(tw, tx, a, splits, budget, stream)                    \

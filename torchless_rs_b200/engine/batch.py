@@ -23,6 +23,7 @@ class StepBatch:
     is_decode: bool
     max_new: int
     max_len: int
+    len_bucket: int       # max_len rounded up to a power of two (at least 256)
     tokens: torch.Tensor
     token_seq: torch.Tensor
     token_pos: torch.Tensor
@@ -67,17 +68,24 @@ class BatchStager:
 
     FIELDS = ("tokens", "token_seq", "token_pos", "seq_slot", "seq_start", "seq_len", "want_rows")
 
+    RING = 4   # pinned buffers in rotation, so the host can prepare a step while earlier copies run
+
     def __init__(self, device: torch.device):
         self.device = device
         self.capacity = 0
-        self.host: Optional[torch.Tensor] = None
+        self.hosts: List[torch.Tensor] = []
+        self.events: List[Optional[torch.cuda.Event]] = []
+        self.turn = 0
         self.dev: Optional[torch.Tensor] = None
 
     def _ensure(self, n: int) -> None:
         if n <= self.capacity:
             return
         cap = max(4096, 1 << (n - 1).bit_length())
-        self.host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+        if self.capacity:
+            torch.cuda.synchronize(self.device)
+        self.hosts = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(self.RING)]
+        self.events = [None] * self.RING
         self.dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         self.capacity = cap
 
@@ -89,15 +97,23 @@ class BatchStager:
             offs.append(total)
             total += (s + 3) // 4 * 4
         self._ensure(max(total, 1))
-        hv = self.host.numpy()
+        self.turn = (self.turn + 1) % self.RING
+        if self.events[self.turn] is not None:
+            self.events[self.turn].synchronize()   # the copy that last used this buffer is done
+        host = self.hosts[self.turn]
+        hv = host.numpy()
         for f, o, s in zip(self.FIELDS, offs, sizes):
             hv[o:o + s] = arrays[f]
-        self.dev[:total].copy_(self.host[:total], non_blocking=True)
+        self.dev[:total].copy_(host[:total], non_blocking=True)
+        ev = self.events[self.turn] or torch.cuda.Event()
+        ev.record()
+        self.events[self.turn] = ev
         views = {f: self.dev[o:o + s] for f, o, s in zip(self.FIELDS, offs, sizes)}
         counts = np.diff(arrays["seq_start"])
+        max_len = int(arrays["seq_len"].max()) if sizes[5] else 0
         return StepBatch(
             n_tokens=sizes[0], n_seqs=sizes[3], n_want=sizes[6], is_decode=is_decode,
             max_new=int(counts.max()) if len(counts) else 0,
-            max_len=int(arrays["seq_len"].max()) if sizes[5] else 0,
+            max_len=max_len, len_bucket=max(256, 1 << max(max_len - 1, 0).bit_length()),
             slots=list(slots), past_lens=list(past_lens),
             new_lens=[int(x) for x in arrays["seq_len"]], **views)

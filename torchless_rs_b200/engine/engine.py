@@ -26,7 +26,8 @@ class Engine:
     sequence's count rounded up to a multiple of 64; it sizes the cache."""
 
     def __init__(self, spec: ModelSpec, weights, rt: Runtime, max_tokens: int,
-                 max_batch: Optional[int] = None, max_seq_len: Optional[int] = None):
+                 max_batch: Optional[int] = None, max_seq_len: Optional[int] = None,
+                 use_graphs: bool = True):
         self.spec = spec
         self.rt = rt
         self.model = DecoderModel(spec, rt)
@@ -36,6 +37,9 @@ class Engine:
         self.model.bind_cache(self.cache)
         self.stager = BatchStager(rt.device)
         self.vocab_size = spec.vocab_size
+        self.use_graphs = use_graphs
+        self._graphs = {}      # key -> (CUDA graph, logits view)
+        self._seen = set()     # keys that have run once without a graph
 
     # ---- sequences -------------------------------------------------------------------
     def start_sequences(self, count: int) -> List[int]:
@@ -79,6 +83,33 @@ class Engine:
         new_lens = [p + c for p, c in zip(past, counts)]
         self.cache.prepare(slots, new_lens)
         batch = self.stager.stage(arrays, slots, past, is_decode=all(c == 1 for c in counts))
-        logits = self.model.forward(batch)
+        logits = self._forward(batch)
         self.cache.commit(slots, new_lens)
+        return logits
+
+    def _forward(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        """Decode steps of one shape launch the same kernels with the same arguments
+        (token ids, positions and page tables are read from device memory), so the
+        second step of a shape is recorded as a CUDA graph and later ones replay it."""
+        if not (self.use_graphs and batch.is_decode):
+            return self.model.forward(batch)
+        key = (batch.n_seqs, batch.n_want, batch.len_bucket, self.rt.workspace.generation,
+               batch.tokens.data_ptr())
+        hit = self._graphs.get(key)
+        if hit is not None:
+            hit[0].replay()
+            return hit[1]
+        if key not in self._seen:
+            self._seen.add(key)
+            return self.model.forward(batch)
+        if len(self._graphs) > 64:
+            self._graphs.clear()
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(batch)
+        if self.rt.workspace.generation != key[3]:   # a buffer moved while recording
+            return self.model.forward(batch)
+        self._graphs[key] = (graph, logits, batch)
+        graph.replay()
         return logits

@@ -17,6 +17,7 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.generation = 0   # goes up whenever a buffer moves; recorded CUDA graphs are then stale
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -27,6 +28,7 @@ class Workspace:
         if buf is None or buf.numel() < n:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[:n].view(*shape)
 
     def bytes_held(self) -> int:
