@@ -314,3 +314,34 @@ def test_gemm_tensor_core(M, N, K):
     assert g.run(a, w[:N], c5, 0)
     assert torch.equal(c, c5)
     assert g.take_error() == 0
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, None), (8, 2, 128, 100), (4, 4, 64, 33),
+                                               (3, 1, 32, None), (6, 3, 64, 64)])
+def test_attention_prefill_bf16(nh, nkv, hd, window):
+    """Tensor-core prefill kernel: sequences from scratch and continuing ones, lengths
+    around the 16-query warps, the 64-query tiles and the 32-key groups."""
+    from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
+    dtype = torch.bfloat16
+    att = AttentionBf16.get(hd)
+    lens = [1, 17, 64, 65, 200, 331, 150]
+    new = [1, 17, 64, 65, 200, 131, 1]      # the last two continue an existing sequence
+    pc = Paged(lens, nkv, hd, dtype, 90 + hd)
+    B, T = len(lens), sum(new)
+    q = _rand((T, nh * hd), dtype, 91)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    seq_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    att.prefill(q, pc.k_pages, pc.v_pages, out, seq_start, seq_len, pc.seq_slot, pc.table, B,
+                max(new), nh, nkv, window, scale)
+    got = out.cpu().double().view(T, nh, hd)
+    qc = q.cpu().view(T, nh, hd)
+    for b in range(B):
+        for i in range(new[b]):
+            tkn, pos = starts[b] + i, lens[b] - new[b] + i
+            ref = attention_reference(qc[tkn], pc.k[b], pc.v[b], pos, window, scale)
+            assert torch.allclose(got[tkn], ref, **_attn_tol(dtype)), f"seq {b} pos {pos}"

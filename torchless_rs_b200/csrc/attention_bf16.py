@@ -17,7 +17,8 @@ MAX_GROUP = 16        # query heads per key/value head that one instruction's ro
 TARGET_BLOCKS = 592   # 148 SMs x 2 resident blocks x 2 waves
 
 for _hd in FAST_HEAD_DIMS:
-    build.register_library(f"attn_bf16_hd{_hd}", ("attention_decode_bf16.cu",),
+    build.register_library(f"attn_bf16_hd{_hd}",
+                           ("attention_decode_bf16.cu", "attention_prefill_bf16.cu"),
                            (f"-DHEAD_DIM={_hd}",))
     # the same kernels with a fixed scratch array inside the library, for callers that must
     # not allocate (see attention_decode_noalloc.h); nothing in this package loads it
@@ -52,6 +53,8 @@ class AttentionBf16:
             self._decode.restype = c_int
             self._scratch = getattr(self.lib, f"tl_attn_decode_scratch_floats_hd{head_dim}")
             self._scratch.restype = c_longlong
+            self._prefill = getattr(self.lib, f"tl_attn_prefill_hd{head_dim}")
+            self._prefill.restype = c_int
 
     def decode(self, q, k_pages, v_pages, out, seq_len, seq_slot, page_table, nh, nkv, window,
                scale, n_splits, workspace) -> None:
@@ -69,6 +72,20 @@ class AttentionBf16:
                             c_int(window or 0), c_float(scale), c_int(n_splits), _stream()),
                "attn_decode")
 
+    def prefill(self, q, k_pages, v_pages, out, seq_start, seq_len, seq_slot, page_table, n_seqs,
+                max_new, nh, nkv, window, scale) -> None:
+        """The new tokens of each sequence (packed, `seq_start` offsets) against the cache,
+        which already holds their keys and values."""
+        if self.lib is None:
+            raise KernelError(f"no tensor-core prefill attention for head size {self.head_dim}")
+        for t, n in ((q, "q"), (k_pages, "k pages"), (v_pages, "v pages"), (out, "out")):
+            _need(t, torch.bfloat16, f"attn prefill {n}")
+        _check(self._prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(seq_start),
+                             _ptr(seq_len), _ptr(seq_slot), _ptr(page_table),
+                             c_int(page_table.stride(0)), c_int(n_seqs), c_int(max_new), c_int(nh),
+                             c_int(nkv), c_int(window or 0), c_float(scale), _stream()),
+               "attn_prefill")
+
     def run(self, q, cache_view, out, batch, nh, nkv, window, scale, workspace) -> bool:
         if self.lib is None or nh // nkv > MAX_GROUP:
             return False
@@ -78,4 +95,7 @@ class AttentionBf16:
                         batch.seq_slot, cache_view.page_table, nh, nkv, window, scale, n_splits,
                         workspace)
             return True
-        return False
+        self.prefill(q, cache_view.k_pages, cache_view.v_pages, out, batch.seq_start, batch.seq_len,
+                     batch.seq_slot, cache_view.page_table, batch.n_seqs, batch.max_new, nh, nkv,
+                     window, scale)
+        return True
