@@ -1,0 +1,295 @@
+"""Each part of a layer alone against its plain counterpart; the layer order as data
+(a layer named twice, a layer that reads another layer's cache); and a toy mixer with
+state of its own, defined here, registered, built and stepped without a change to the
+package's files."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import mistral_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _rt(dtype):
+    from torchless_rs_b200.parts.runtime import Runtime
+    return Runtime("cuda:0", dtype)
+
+
+def _tol(dtype):
+    return dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+def _weights(expected, seed, dtype=torch.bfloat16):
+    from torchless_rs_b200.weights import random_tensors
+    return dict(random_tensors(expected, seed, dtype))
+
+
+def _np(weights):
+    return {k: v.float().numpy() for k, v in weights.items()}
+
+
+class FakeBatch:
+    """The fields of a step that parts read, for one sequence from position 0."""
+
+    def __init__(self, n, slot=0, past=0, dev="cuda:0"):
+        i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)
+        self.n_tokens, self.n_seqs, self.is_decode = n, 1, n == 1
+        self.max_new, self.max_len = n, past + n
+        self.len_bucket = max(256, 1 << (past + n - 1).bit_length())
+        self.token_seq, self.token_pos = i32([0] * n), i32(list(range(past, past + n)))
+        self.seq_slot, self.seq_start, self.seq_len = i32([slot]), i32([0, n]), i32([past + n])
+        self.slots, self.past_lens, self.new_lens = [slot], [past], [past + n]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part(dtype):
+    from torchless_rs_b200.config import PartSpec
+    from torchless_rs_b200.parts import lookup
+    rt = _rt(dtype)
+    spec = PartSpec("rmsnorm", {"size": 72, "eps": 3e-4})
+    cls = lookup("norm", "rmsnorm")
+    w = _weights(cls.expected_tensors(spec, "x.norm"), 1)
+    part = cls(spec, "x.norm", rt)
+    part.load(w)
+    x = torch.randn((9, 72), generator=torch.Generator().manual_seed(2)) * 2
+    out = torch.empty((9, 72), dtype=dtype, device="cuda:0")
+    part(x.cuda(), out)
+    ref = plain.rmsnorm(x.numpy(), _np(w)["x.norm.weight"], 3e-4)
+    assert np.allclose(out.float().cpu().numpy(), ref, **_tol(dtype))
+
+
+def test_position_part():
+    from torchless_rs_b200.config import PartSpec
+    from torchless_rs_b200.parts import lookup
+    for hd, theta in ((16, 1e4), (128, 1e6), (48, 5e4)):
+        part = lookup("position", "rope_half_split")(PartSpec("rope_half_split", {"head_dim": hd, "theta": theta}),
+                                                     _rt(torch.float32))
+        assert part.style == 0
+        assert np.array_equal(part.inv_freq.cpu().numpy(), plain.rope_inv_freq(hd, theta))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_feed_forward_part(dtype):
+    from torchless_rs_b200.config import PartSpec
+    from torchless_rs_b200.parts import lookup
+    rt = _rt(dtype)
+    spec = PartSpec("swiglu", {"hidden_size": 80, "intermediate_size": 200})
+    cls = lookup("feed_forward", "swiglu")
+    w = _weights(cls.expected_tensors(spec, "m"), 3)
+    part = cls(spec, "m", rt)
+    part.load(w)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn((11, 80), generator=g).to(dtype)
+    res = torch.randn((11, 80), generator=g)
+    r = res.clone().cuda()
+    part.forward(x.cuda(), r, None)
+    wn = _np(w)
+    ref = res.numpy() + plain.swiglu(x.float().numpy(), wn["m.gate_proj.weight"], wn["m.up_proj.weight"],
+                                     wn["m.down_proj.weight"])
+    assert np.allclose(r.cpu().numpy(), ref, **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 7), (6, 3, 32, None), (4, 1, 64, 50)])
+def test_attention_part(dtype, nh, nkv, hd, window):
+    """The mixer alone with a cache of its own: a prompt, then token by token."""
+    from torchless_rs_b200.cache import Cache
+    from torchless_rs_b200.config import PartSpec
+    from torchless_rs_b200.parts import lookup
+    rt = _rt(dtype)
+    H, theta, n = 96, 1e4, 90
+    spec = PartSpec("attention", {"hidden_size": H, "num_heads": nh, "num_kv_heads": nkv,
+                                  "head_dim": hd, "window": window})
+    pos = lookup("position", "rope_half_split")(PartSpec("rope_half_split", {"head_dim": hd, "theta": theta}), rt)
+    cls = lookup("mixer", "attention")
+    w = _weights(cls.expected_tensors(spec, "a"), 5)
+    part = cls(spec, "a", rt, position=pos)
+    part.load(w)
+    cache = Cache([part.cache_request()], 256, 2, None, dtype, "cuda:0")
+    part.bind_cache(cache.view(0))
+    (slot,) = cache.acquire(1)
+    x = torch.randn((n, H), generator=torch.Generator().manual_seed(6)).to(dtype)
+    got = []
+    for past, cnt in [(0, 70)] + [(i, 1) for i in range(70, n)]:
+        cache.prepare([slot], [past + cnt])
+        res = torch.zeros((cnt, H), dtype=torch.float32, device="cuda:0")
+        part.forward(x[past:past + cnt].cuda().contiguous(), res, FakeBatch(cnt, slot, past))
+        cache.commit([slot], [past + cnt])
+        got.append(res.cpu().numpy())
+    wn = _np(w)
+    ref, _ = plain.attention_mixer(x.float().numpy(), wn["a.q_proj.weight"], wn["a.k_proj.weight"],
+                                   wn["a.v_proj.weight"], wn["a.o_proj.weight"], np.arange(n), nh, nkv,
+                                   hd, theta, window)
+    assert np.allclose(np.concatenate(got), ref, **_tol(dtype))
+
+
+# ---------------------------------------------------------------------------
+# the order of layers and shared caches are data
+# ---------------------------------------------------------------------------
+def _engine(spec, seed, dtype, max_tokens=512):
+    from torchless_rs_b200.engine.engine import Engine
+    from torchless_rs_b200.engine.model import expected_tensors
+    w = _weights(expected_tensors(spec), seed)
+    return Engine(spec, w, _rt(dtype), max_tokens), _np(w)
+
+
+def _plain_layer(h, wn, prefix, cfg, window, positions, kv=None):
+    lw = {k[len(prefix) + 1:]: v for k, v in wn.items() if k.startswith(prefix + ".")}
+    a, kv_out = plain.attention_mixer(
+        plain.rmsnorm(h, lw["input_layernorm.weight"], cfg.rms_norm_eps),
+        lw["self_attn.q_proj.weight"], lw.get("self_attn.k_proj.weight"), lw.get("self_attn.v_proj.weight"),
+        lw["self_attn.o_proj.weight"], positions, cfg.num_attention_heads, cfg.num_key_value_heads,
+        cfg.head_dim, cfg.rope_theta, window, kv_override=kv)
+    h = h + a
+    m = plain.swiglu(plain.rmsnorm(h, lw["post_attention_layernorm.weight"], cfg.rms_norm_eps),
+                     lw["mlp.gate_proj.weight"], lw["mlp.up_proj.weight"], lw["mlp.down_proj.weight"])
+    return h + m, kv_out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layer_named_twice_and_layer_reading_another_cache(dtype):
+    """Three layers: 0 has a window, 1 reads the cache of layer 0 (it has no k and v
+    matrices of its own), 2 sees all keys; the order runs layer 2 twice."""
+    from dataclasses import replace
+    from tiny import TINY_D
+    from torchless_rs_b200.config import ModelSpec, config_from_dict
+    from torchless_rs_b200.engine.model import expected_tensors
+    cfg = config_from_dict(dict(TINY_D, num_hidden_layers=3, layer_types=["sliding_attention"] * 2 + ["full_attention"]))
+    base = cfg.model_spec()
+    layers = list(base.layers)
+    layers[1] = replace(layers[1], cache_from=0)
+    spec = ModelSpec(base.hidden_size, base.vocab_size, base.embedding_name, base.head_name, False,
+                     base.final_norm, base.final_norm_prefix, tuple(layers), (0, 1, 2, 2))
+    names = expected_tensors(spec)
+    assert "model.layers.1.self_attn.k_proj.weight" not in names
+    eng, wn = _engine(spec, 7, dtype)
+    assert len(eng.cache.paged) == 2 and eng.cache.paged[0].layers == [0]
+    toks = [int(t) for t in np.random.default_rng(3).integers(0, cfg.vocab_size, 100)]
+    (s,) = eng.start_sequences(1)
+    got = [eng.step([s], [toks[:60]], "all").cpu().numpy().copy()]
+    for t in toks[60:]:
+        got.append(eng.step([s], [[t]], "last").cpu().numpy().copy())
+    eng.end_sequences([s])
+    # the same by hand with the plain parts
+    pos = np.arange(len(toks))
+    h = plain.embedding(wn["model.embed_tokens.weight"], toks)
+    h, kv0 = _plain_layer(h, wn, "model.layers.0", cfg, cfg.sliding_window, pos)
+    h, _ = _plain_layer(h, wn, "model.layers.1", cfg, cfg.sliding_window, pos, kv=kv0)
+    h, _ = _plain_layer(h, wn, "model.layers.2", cfg, None, pos)
+    h, _ = _plain_layer(h, wn, "model.layers.2", cfg, None, pos)
+    ref = plain.rmsnorm(h, wn["model.norm.weight"], cfg.rms_norm_eps) @ wn["lm_head.weight"].T
+    g = np.concatenate(got)
+    if dtype == torch.float32:
+        assert np.abs(g - ref).max() < 5e-5 + 1e-4 * np.abs(ref).max()
+    else:
+        assert np.abs(g - ref).max() < 2.5e-2 * np.abs(ref).max()
+
+
+# ---------------------------------------------------------------------------
+# a toy mixer with state of its own, defined and registered here
+# ---------------------------------------------------------------------------
+def _register_toy():
+    from torchless_rs_b200.cache import StateRequest
+    from torchless_rs_b200.parts import register_mixer
+    from torchless_rs_b200.weights import TensorSpec
+
+    @register_mixer("toy_decay")
+    class ToyDecay:
+        """state_t = decay * state_{t-1} + W_in x_t;  out_t = W_out state_t.  The state
+        [width] of each sequence lives in the cache's fixed-size per-sequence storage."""
+
+        def __init__(self, spec, prefix, rt, position=None):
+            self.h, self.width, self.decay = spec.params["hidden_size"], spec.params["width"], spec.params["decay"]
+            self.prefix, self.rt, self.state = prefix, rt, None
+
+        @classmethod
+        def expected_tensors(cls, spec, prefix):
+            h, w = spec.params["hidden_size"], spec.params["width"]
+            return {f"{prefix}.in.weight": TensorSpec((w, h)), f"{prefix}.out.weight": TensorSpec((h, w))}
+
+        def load(self, weights):
+            self.w_in = weights[f"{self.prefix}.in.weight"].float().to(self.rt.device)
+            self.w_out = weights[f"{self.prefix}.out.weight"].float().to(self.rt.device)
+
+        def cache_request(self):
+            return StateRequest((self.width,), torch.float32)
+
+        def bind_cache(self, view):
+            self.state = view          # [slots, width]
+
+        def forward(self, xn, residual, batch):
+            u = xn.float() @ self.w_in.T
+            start = 0
+            for slot, past, new in zip(batch.slots, batch.past_lens, batch.new_lens):
+                st = self.state[slot]
+                for i in range(start, start + new - past):
+                    st.mul_(self.decay).add_(u[i])
+                    residual[i] += self.w_out @ st
+                start += new - past
+    return ToyDecay
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_mixer_with_state(dtype):
+    from dataclasses import replace
+    from tiny import TINY_B
+    from torchless_rs_b200.config import ModelSpec, PartSpec, config_from_dict
+    _register_toy()
+    cfg = config_from_dict(dict(TINY_B, num_hidden_layers=3))
+    base = cfg.model_spec()
+    toy = PartSpec("toy_decay", {"hidden_size": cfg.hidden_size, "width": 24, "decay": 0.9})
+    layers = list(base.layers)
+    layers[1] = replace(layers[1], mixer=toy, position=None)
+    spec = ModelSpec(base.hidden_size, base.vocab_size, base.embedding_name, base.head_name, False,
+                     base.final_norm, base.final_norm_prefix, tuple(layers), base.order)
+    eng, wn = _engine(spec, 9, dtype)
+    assert len(eng.cache.states) == 1 and eng.cache.states[0].layers == [1]
+    assert not eng.model.graph_safe                      # the toy reads host values: no graph replay
+    rng = np.random.default_rng(4)
+    reqs = [[int(t) for t in rng.integers(0, cfg.vocab_size, n)] for n in (30, 12)]
+
+    def reference(toks):
+        pos = np.arange(len(toks))
+        h = plain.embedding(wn["model.embed_tokens.weight"], toks)
+        h, _ = _plain_layer(h, wn, "model.layers.0", cfg, None, pos)
+        x = plain.rmsnorm(h, wn["model.layers.1.input_layernorm.weight"], cfg.rms_norm_eps)
+        u = x @ wn["model.layers.1.self_attn.in.weight"].T
+        st, outs = np.zeros(24, dtype=np.float32), []
+        for i in range(len(toks)):
+            st = 0.9 * st + u[i]
+            outs.append(wn["model.layers.1.self_attn.out.weight"] @ st)
+        h = h + np.stack(outs)
+        lw = {k[len("model.layers.1."):]: v for k, v in wn.items() if k.startswith("model.layers.1.")}
+        h = h + plain.swiglu(plain.rmsnorm(h, lw["post_attention_layernorm.weight"], cfg.rms_norm_eps),
+                             lw["mlp.gate_proj.weight"], lw["mlp.up_proj.weight"], lw["mlp.down_proj.weight"])
+        h, _ = _plain_layer(h, wn, "model.layers.2", cfg, None, pos)
+        return plain.rmsnorm(h, wn["model.norm.weight"], cfg.rms_norm_eps) @ wn["lm_head.weight"].T
+
+    # a batch of two that start together with unequal prompts, then go on token by token;
+    # afterwards the first slot is used again and must start from a zero state
+    for round_ in range(2):
+        slots = eng.start_sequences(2)
+        pre = [7, 3]
+        out = eng.step(slots, [r[:p] for r, p in zip(reqs, pre)], "all").cpu().numpy().copy()
+        got = [[out[:7]], [out[7:10]]]
+        fed, live = list(pre), [0, 1]
+        while live:
+            done = [i for i in live if fed[i] >= len(reqs[i])]
+            if done:
+                eng.end_sequences([slots[i] for i in done])
+                live = [i for i in live if i not in done]
+                continue
+            out = eng.step([slots[i] for i in live], [[reqs[i][fed[i]]] for i in live], "last").cpu().numpy().copy()
+            for j, i in enumerate(live):
+                got[i].append(out[j:j + 1])
+                fed[i] += 1
+        for i, r in enumerate(reqs):
+            ref, g = reference(r), np.concatenate(got[i])
+            bound = 5e-5 + 1e-4 * np.abs(ref).max() if dtype == torch.float32 else 2.5e-2 * np.abs(ref).max()
+            assert np.abs(g - ref).max() < bound, f"round {round_} request {i}"
+    assert eng.cache.slots.held_count == 0

@@ -139,8 +139,8 @@ class StateGroup:
 
 
 class Cache:
-    """`requests[i]` is what layer i's mixer asks for (None: nothing, or it reads
-    another layer's cache).  `max_tokens` is the most tokens that live sequences hold
+    """`requests[k]` is what the mixer of the k-th entry of the layer order asks for
+    (None: nothing, or it reads another entry's cache); "layer" below means such an entry.  `max_tokens` is the most tokens that live sequences hold
     at any time, each sequence's count rounded up to a multiple of PAGE."""
 
     def __init__(self, requests: Sequence[Union[PagedKVRequest, StateRequest, None]],

@@ -91,7 +91,7 @@ class Engine:
         """Decode steps of one shape launch the same kernels with the same arguments
         (token ids, positions and page tables are read from device memory), so the
         second step of a shape is recorded as a CUDA graph and later ones replay it."""
-        if not (self.use_graphs and batch.is_decode):
+        if not (self.use_graphs and batch.is_decode and self.model.graph_safe):
             return self.model.forward(batch)
         key = (batch.n_seqs, batch.n_want, batch.len_bucket, self.rt.workspace.generation,
                batch.tokens.data_ptr())

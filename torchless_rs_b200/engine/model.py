@@ -67,6 +67,10 @@ class DecoderModel:
             spec.final_norm, spec.final_norm_prefix, rt)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
+        # a part whose forward reads host-side values of the batch cannot be replayed from a
+        # recorded graph; it says so by not setting `graph_safe`
+        self.graph_safe = all(getattr(p, "graph_safe", False)
+                              for b in self.blocks for p in (b.mixer, b.feed_forward))
 
     # ---- weights ---------------------------------------------------------------------
     def tensors(self) -> Dict[str, TensorSpec]:
@@ -97,13 +101,19 @@ class DecoderModel:
         return total
 
     # ---- cache ------------------------------------------------------------------------
+    # A cache belongs to a place in the order, not to a layer: a layer that is named twice
+    # runs twice per token and keeps keys and values of both passes apart.
     def cache_requests(self) -> List[object]:
-        return [m.cache_request() for m in self.mixers]
+        """One request per entry of the order (None where the entry keeps no cache)."""
+        return [self.mixers[i].cache_request() for i in self.spec.order]
 
     def bind_cache(self, cache) -> None:
-        for i, (layer, m) in enumerate(zip(self.spec.layers, self.mixers)):
-            src = layer.cache_from if layer.cache_from is not None else i
-            m.bind_cache(cache.view(src))
+        self.views = []
+        last_run = {}     # layer -> the latest entry of the order that ran it
+        for k, i in enumerate(self.spec.order):
+            src = self.spec.layers[i].cache_from
+            self.views.append(cache.view(k) if src is None else cache.view(last_run[src]))
+            last_run[i] = k
 
     # ---- one step -----------------------------------------------------------------------
     def forward(self, batch) -> Optional[torch.Tensor]:
@@ -113,7 +123,8 @@ class DecoderModel:
         T, H = batch.n_tokens, self.spec.hidden_size
         x = ws.get("stream", (T, H), torch.float32)
         rt.ops.embed(batch.tokens, self.embedding, x)
-        for i in self.spec.order:
+        for k, i in enumerate(self.spec.order):
+            self.mixers[i].bind_cache(self.views[k])
             self.blocks[i].forward(x, batch)
         if batch.n_want == 0:
             return None

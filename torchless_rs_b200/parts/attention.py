@@ -32,6 +32,8 @@ class Attention:
     it asks of the cache, or None), `bind_cache(view)` (the view of its own layer or
     of the layer it reads), and `forward(xn, residual, batch)`, which adds its
     output to the 32-bit `residual` in place."""
+    graph_safe = True   # forward launches kernels whose arguments do not depend on host values
+
 
     def __init__(self, spec: PartSpec, prefix: str, rt: Runtime, position=None):
         p = spec.params

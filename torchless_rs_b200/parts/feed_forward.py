@@ -21,6 +21,8 @@ class SwiGLU:
     """Parameters: `hidden_size`, `intermediate_size`.  Interface of every
     feed-forward: `expected_tensors(spec, prefix)` (a class method), `load(weights)`, and `forward(xn, residual, batch)`,
     which adds its output to the 32-bit `residual` in place."""
+    graph_safe = True   # forward launches kernels whose arguments do not depend on host values
+
 
     def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
         self.hidden = int(spec.params["hidden_size"])
