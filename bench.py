@@ -149,34 +149,22 @@ def decode_device_timed(model, batch: int, steps: int, warmup: int, end_context:
 
 
 def decode_end_to_end(model, batch: int, steps: int, warmup: int, end_context: int):
-    """The same through `Model.generate`: host token ids in, host token ids out at
-    every step.  The context is put in place first; the time runs from the first
-    emitted token (after the one-token 'prompt' step and warm-up) to the last."""
+    """The same through `Model.generate`: host token ids in, host token ids out at every
+    step.  Real prompts are prefilled first (not timed); the time runs on the host from
+    the token emitted after `warmup` decode steps to the last one, with a device
+    synchronisation at each stamp."""
     import torch
     eng = model.engine
-    start = end_context - steps - warmup - 1
-    slots = fill_context(model, batch, start)
-    # generate() takes its own slots; hand it sequences that already hold a context by
-    # wrapping the engine's start_sequences for this one call
+    n_prompt = end_context - steps - warmup - 1
+    prompts = [[(11 * i + 5 * j + 3) % eng.vocab_size for j in range(n_prompt)] for i in range(batch)]
     stamps = []
-    taken = {"done": False}
-    orig = eng.start_sequences
 
-    def start_sequences(count):
-        assert count == batch and not taken["done"]
-        taken["done"] = True
-        return slots
-    eng.start_sequences = start_sequences
-    try:
-        prompts = [[(11 * i + 5) % eng.vocab_size] for i in range(batch)]
-        def on_token(i, tok):
-            if i == batch - 1:
-                torch.cuda.synchronize()
-                stamps.append(time.perf_counter())
-        model.generate(prompts, max_tokens=steps + warmup + 1, temperature=0.0, stop_ids=(),
-                       on_token=on_token)
-    finally:
-        eng.start_sequences = orig
+    def on_token(i, tok):
+        if i == batch - 1:
+            torch.cuda.synchronize()
+            stamps.append(time.perf_counter())
+    model.generate(prompts, max_tokens=steps + warmup + 1, temperature=0.0, stop_ids=(),
+                   on_token=on_token)
     dt = stamps[-1] - stamps[warmup]
     n = len(stamps) - 1 - warmup
     return batch * n / dt, 1e3 * dt / n

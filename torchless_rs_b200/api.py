@@ -40,10 +40,17 @@ class Model:
     `engine` gives `step`, `start_sequences`, `end_sequences`."""
 
     def __init__(self, config, engine: Engine):
-        from .sampling.sampler import Sampler
         self.config = config
         self.engine = engine
-        self.sampler = Sampler(engine.rt.device)
+        self._sampler = None
+
+    @property
+    def sampler(self):
+        """Built at first use, so that replaying logits never compiles the sampling kernels."""
+        if self._sampler is None:
+            from .sampling.sampler import Sampler
+            self._sampler = Sampler(self.engine.rt.device)
+        return self._sampler
 
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 16,
                  temperature: float = 0.0, top_k: Optional[int] = None,
@@ -99,9 +106,6 @@ def from_random(config, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat1
     adt = parse_dtype(dtype)
     rt = Runtime(device, adt)
 
-    class _Lazy(dict):
-        def __missing__(self, name):
-            return None
     exp = expected_tensors(spec)
     weights = {n: t for n, t in random_tensors(exp, seed, adt, rt.device)}
     engine = Engine(spec, weights, rt, max_tokens or _default_max_tokens(config), max_batch,

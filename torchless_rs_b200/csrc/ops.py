@@ -35,6 +35,12 @@ def launches() -> int:
     return _counter["launches"]
 
 
+def add_launches(n: int) -> None:
+    """Counts kernels that ran without passing through this module: a replayed CUDA
+    graph launches the kernels that were counted while it was recorded."""
+    _counter["launches"] += n
+
+
 def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 

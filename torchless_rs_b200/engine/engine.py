@@ -14,6 +14,7 @@ import torch
 
 from ..cache import Cache
 from ..config.spec import ModelSpec
+from ..csrc import ops
 from ..parts.runtime import Runtime
 from .batch import BatchStager, StepBatch, layout_step
 from .model import DecoderModel
@@ -98,6 +99,7 @@ class Engine:
         hit = self._graphs.get(key)
         if hit is not None:
             hit[0].replay()
+            ops.add_launches(hit[3])
             return hit[1]
         if key not in self._seen:
             self._seen.add(key)
@@ -106,10 +108,14 @@ class Engine:
             self._graphs.clear()
         graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
+        before = ops.launches()
         with torch.cuda.graph(graph):
             logits = self.model.forward(batch)
+        recorded = ops.launches() - before    # recording launches nothing; replay runs them all
+        ops.add_launches(-recorded)
         if self.rt.workspace.generation != key[3]:   # a buffer moved while recording
             return self.model.forward(batch)
-        self._graphs[key] = (graph, logits, batch)
+        self._graphs[key] = (graph, logits, batch, recorded)
         graph.replay()
+        ops.add_launches(recorded)
         return logits
