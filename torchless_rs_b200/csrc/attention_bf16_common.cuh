@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 #ifndef HEAD_DIM
 #define HEAD_DIM 128
 #endif

@@ -31,6 +31,8 @@ FN(attn_decode_kernel)(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        int window, float scale_log2, int n_splits) {
   __shared__ float sm_o[WARPS][HI ? 16 : 8][HEAD_DIM];
   __shared__ float sm_m[WARPS][16], sm_l[WARPS][16];
+  pdl_wait();
+  pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -173,6 +175,8 @@ FN(attn_decode_kernel)(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 __global__ void __launch_bounds__(HEAD_DIM)
 FN(attn_decode_combine_kernel)(const float* __restrict__ part, __nv_bfloat16* __restrict__ out,
                                int nh, int n_splits) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const float* src = part + ((size_t)b * nh + h) * n_splits * PART_STRIDE;
   float m = -INFINITY;
@@ -205,17 +209,16 @@ extern "C" int FN(tl_attn_decode)(const void* q, const void* k_pages, const void
     return -2;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(n_splits, nkv, B);
+  int st;
   if (nh / nkv > 8)
-    FN(attn_decode_kernel)<true><<<grid, WARPS * 32, 0, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, part,
-        seq_len, seq_slot, page_table, table_stride, nh, nkv, window, scale_log2, n_splits);
+    st = tl_launch(FN(attn_decode_kernel)<true>, grid, dim3(WARPS * 32), 0, stream,
+                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+                   part, seq_len, seq_slot, page_table, table_stride, nh, nkv, window, scale_log2, n_splits);
   else
-    FN(attn_decode_kernel)<false><<<grid, WARPS * 32, 0, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, part,
-        seq_len, seq_slot, page_table, table_stride, nh, nkv, window, scale_log2, n_splits);
-  int st = (int)cudaGetLastError();
+    st = tl_launch(FN(attn_decode_kernel)<false>, grid, dim3(WARPS * 32), 0, stream,
+                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+                   part, seq_len, seq_slot, page_table, table_stride, nh, nkv, window, scale_log2, n_splits);
   if (st) return st;
-  FN(attn_decode_combine_kernel)<<<dim3(nh, B), HEAD_DIM, 0, stream>>>(
-      part, (__nv_bfloat16*)out, nh, n_splits);
-  return (int)cudaGetLastError();
+  return tl_launch(FN(attn_decode_combine_kernel), dim3(nh, B), dim3(HEAD_DIM), 0, stream,
+                   (const float*)part, (__nv_bfloat16*)out, nh, n_splits);
 }

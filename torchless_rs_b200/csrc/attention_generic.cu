@@ -45,6 +45,8 @@ attn_generic_kernel(const act_t* __restrict__ q, const act_t* __restrict__ k_pag
   __shared__ float ps[ATT_THREADS];
   __shared__ int pg[ATT_THREADS];  // page of each key of the chunk
   __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int kvh = h / (nh / nkv);
   const int pos = token_pos[t];
@@ -114,8 +116,7 @@ extern "C" int TL_NAME(tl_attn_generic)(const void* q, const void* k_pages, cons
   if (T <= 0) return 0;
   if (hd % 16 != 0 || hd < 16 || hd > MAX_HD || nkv <= 0 || nh % nkv != 0) return TL_ERR_UNSUPPORTED;
   dim3 grid(T, nh);
-  attn_generic_kernel<<<grid, ATT_THREADS, 0, stream>>>(
-      (const act_t*)q, (const act_t*)k_pages, (const act_t*)v_pages, (act_t*)out, token_pos,
-      token_seq, seq_slot, page_table, table_stride, nh, nkv, hd, window, scale);
-  return TL_LAUNCH_STATUS();
+  return tl_launch(attn_generic_kernel, grid, dim3(ATT_THREADS), 0, stream, (const act_t*)q,
+                   (const act_t*)k_pages, (const act_t*)v_pages, (act_t*)out, token_pos, token_seq,
+                   seq_slot, page_table, table_stride, nh, nkv, hd, window, scale);
 }

@@ -22,6 +22,8 @@ FN(attn_prefill_kernel)(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ seq_start, const int* __restrict__ seq_len,
                         const int* __restrict__ seq_slot, const int* __restrict__ page_table,
                         int table_stride, int nh, int nkv, int window, float scale_log2) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.z, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -149,9 +151,8 @@ extern "C" int FN(tl_attn_prefill)(const void* q, const void* k_pages, const voi
   if (nkv <= 0 || nh % nkv != 0 || nh > 65535 || B > 65535) return -2;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid((max_new + PF_TILE - 1) / PF_TILE, nh, B);
-  FN(attn_prefill_kernel)<<<grid, PF_WARPS * 32, 0, stream>>>(
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
-      (__nv_bfloat16*)out, seq_start, seq_len, seq_slot, page_table, table_stride, nh, nkv, window,
-      scale_log2);
-  return (int)cudaGetLastError();
+  return tl_launch(FN(attn_prefill_kernel), grid, dim3(PF_WARPS * 32), 0, stream,
+                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+                   (__nv_bfloat16*)out, seq_start, seq_len, seq_slot, page_table, table_stride, nh, nkv,
+                   window, scale_log2);
 }

@@ -82,3 +82,5 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   __syncthreads();
   return scratch[32];
 }
+
+#include "pdl.cuh"

@@ -9,6 +9,8 @@
 // ---------------------------------------------------------------------------
 __global__ void embed_kernel(const int* __restrict__ tokens, const act_t* __restrict__ table,
                              float* __restrict__ x, int H, int vocab) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // the host has checked the range already
@@ -20,8 +22,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const act_t* __rest
 extern "C" int TL_NAME(tl_embed)(const int* tokens, const void* table, float* x, int T, int H,
                                  int vocab, cudaStream_t stream) {
   if (T <= 0) return 0;
-  embed_kernel<<<T, 256, 0, stream>>>(tokens, (const act_t*)table, x, H, vocab);
-  return TL_LAUNCH_STATUS();
+  return tl_launch(embed_kernel, dim3(T), dim3(256), 0, stream, tokens, (const act_t*)table, x, H, vocab);
 }
 
 // ---------------------------------------------------------------------------
@@ -33,6 +34,8 @@ template <typename W>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const W* __restrict__ w, act_t* __restrict__ y, int H, float eps) {
   __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
   float ss = 0.0f;
@@ -52,11 +55,10 @@ extern "C" int TL_NAME(tl_rmsnorm)(const float* x, const int* rows, const void* 
   if (n_rows <= 0) return 0;
   const int threads = H >= 2048 ? 512 : 256;
   if (w_is_f32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, (const float*)w, (act_t*)y, H, eps);
-  else
-    rmsnorm_kernel<__nv_bfloat16>
-        <<<n_rows, threads, 0, stream>>>(x, rows, (const __nv_bfloat16*)w, (act_t*)y, H, eps);
-  return TL_LAUNCH_STATUS();
+    return tl_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, rows,
+                     (const float*)w, (act_t*)y, H, eps);
+  return tl_launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, rows,
+                   (const __nv_bfloat16*)w, (act_t*)y, H, eps);
 }
 
 // ---------------------------------------------------------------------------
@@ -82,6 +84,8 @@ __global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
                                         const float* __restrict__ inv_freq, int style, int nh,
                                         int nkv, int hd) {
   // grid (tokens, heads): query heads, then key heads, then value heads
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = token_pos[t];
   const int half = hd >> 1;
@@ -132,11 +136,9 @@ extern "C" int TL_NAME(tl_rope_cache_write)(const float* qkv, int ld, void* q_ou
   const int heads = nh + (k_pages ? 2 * nkv : 0);
   if (heads > 65535) return TL_ERR_UNSUPPORTED;
   dim3 grid(T, heads);
-  rope_cache_write_kernel<<<grid, 64, 0, stream>>>(qkv, ld, (act_t*)q_out, (act_t*)k_pages,
-                                                   (act_t*)v_pages, token_pos, token_seq, seq_slot,
-                                                   page_table, table_stride, inv_freq, style, nh,
-                                                   nkv, hd);
-  return TL_LAUNCH_STATUS();
+  return tl_launch(rope_cache_write_kernel, grid, dim3(64), 0, stream, qkv, ld, (act_t*)q_out,
+                   (act_t*)k_pages, (act_t*)v_pages, token_pos, token_seq, seq_slot, page_table,
+                   table_stride, inv_freq, style, nh, nkv, hd);
 }
 
 // ---------------------------------------------------------------------------
@@ -146,6 +148,8 @@ extern "C" int TL_NAME(tl_rope_cache_write)(const float* qkv, int ld, void* q_ou
 // ---------------------------------------------------------------------------
 __global__ void silu_mul_kernel(const float* __restrict__ gu, act_t* __restrict__ out, int I,
                                 size_t total) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
@@ -159,6 +163,5 @@ extern "C" int TL_NAME(tl_silu_mul)(const float* gu, void* out, int T, int I, cu
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-  silu_mul_kernel<<<blocks, 256, 0, stream>>>(gu, (act_t*)out, I, total);
-  return TL_LAUNCH_STATUS();
+  return tl_launch(silu_mul_kernel, dim3(blocks), dim3(256), 0, stream, gu, (act_t*)out, I, total);
 }

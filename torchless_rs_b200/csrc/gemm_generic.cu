@@ -48,6 +48,8 @@ gemm_tiled_kernel(const act_t* __restrict__ A, int lda, const act_t* __restrict_
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   __shared__ float Us[MODE == MODE_SWIGLU ? BK : 1][BN + 4];
+  pdl_wait();
+  pdl_launch_dependents();
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -128,6 +130,8 @@ template <int MODE, int MB, bool VECTOR>
 __global__ void __launch_bounds__(256)
 gemm_skinny_kernel(const act_t* __restrict__ A, int lda, const act_t* __restrict__ W, int ldw,
                    void* __restrict__ C, int ldc, int M, int N, int K) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (n >= N) return;
@@ -187,25 +191,19 @@ static int launch_mode(const act_t* A, int lda, const act_t* W, int ldw, void* C
                      ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
     const int warps = 8;
     dim3 grid((N + warps - 1) / warps), block(warps * 32);
-#define SKINNY(MB)                                                                              \
-  do {                                                                                          \
-    if (vec)                                                                                    \
-      gemm_skinny_kernel<MODE, MB, true><<<grid, block, 0, stream>>>(A, lda, W, ldw, C, ldc, M, \
-                                                                     N, K);                     \
-    else                                                                                        \
-      gemm_skinny_kernel<MODE, MB, false><<<grid, block, 0, stream>>>(A, lda, W, ldw, C, ldc,   \
-                                                                      M, N, K);                 \
-  } while (0)
+#define SKINNY(MB)                                                                               \
+  return vec ? tl_launch(gemm_skinny_kernel<MODE, MB, true>, grid, block, 0, stream, A, lda, W,  \
+                         ldw, C, ldc, M, N, K)                                                   \
+             : tl_launch(gemm_skinny_kernel<MODE, MB, false>, grid, block, 0, stream, A, lda, W, \
+                         ldw, C, ldc, M, N, K)
     if (M == 1) SKINNY(1);
     else if (M == 2) SKINNY(2);
     else if (M <= 4) SKINNY(4);
     else SKINNY(8);
 #undef SKINNY
-  } else {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_tiled_kernel<MODE><<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
   }
-  return TL_LAUNCH_STATUS();
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  return tl_launch(gemm_tiled_kernel<MODE>, grid, dim3(256), 0, stream, A, lda, W, ldw, C, ldc, M, N, K);
 }
 
 // N counts output columns; in SwiGLU mode W has 2*N rows.

@@ -28,6 +28,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -218,10 +220,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) pdl_launch_dependents();
 
   if (warp == 4 && lane == 0) {
-    // ---- TMA producer
-    for (int i = 0; i < n_kb; ++i) {
+    // ---- TMA producer.  The weights do not depend on earlier kernels, so the tiles of the
+    // first stages are requested before the wait for those kernels; the activations after it.
+    const int pre = n_kb < stages ? n_kb : stages;
+    for (int i = 0; i < pre; ++i) {
+      uint8_t* st = smem + (size_t)i * STAGE_BYTES;
+      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+      const int k = (kb0 + i) * TILE_K;
+      tma_load_2d(st, &tm_w, &full_bar[i], k, n0);
+      if (SWIGLU) tma_load_2d(st + A_BYTES, &tm_w, &full_bar[i], k, args.N + n0);
+    }
+    pdl_wait();
+    for (int i = 0; i < pre; ++i) {
+      uint8_t* st = smem + (size_t)i * STAGE_BYTES;
+      tma_load_2d(st + A_BYTES * (SWIGLU ? 2 : 1), &tm_x, &full_bar[i], (kb0 + i) * TILE_K, m0);
+    }
+    for (int i = pre; i < n_kb; ++i) {
       const int s = i % stages;
       const uint32_t ph = (uint32_t)(i / stages) & 1u;
       if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) break;
@@ -257,6 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (ok) umma_commit(acc_bar);
   } else if (warp < 4) {
     // ---- epilogue: thread = one weight row = one column of C
+    pdl_wait();   // C may be read and written by earlier kernels
     const bool ok = mbar_wait(acc_bar, 0, abort_flag, 3);
     tc_fence_after();
     const int row = warp * 32 + lane;
@@ -276,16 +294,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             if (SWIGLU) red[(BN + c0 + j) * TILE_N + row] = __uint_as_float(u[j]);
           }
         } else if (n < args.N) {
+          float* cf = (float*)args.C + (size_t)(m0 + c0) * args.ldc + n;
+          __nv_bfloat16* cb = (__nv_bfloat16*)args.C + (size_t)(m0 + c0) * args.ldc + n;
+          const int valid = args.M - (m0 + c0);   // columns of this group that are real tokens
+          if (args.mode == MODE_ACCUM_F32) {
+            float prev[16];   // all loads first, so that they are in flight together
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m >= args.M) break;
-            const float v = __uint_as_float(r[j]);
-            const size_t idx = (size_t)m * args.ldc + n;
-            if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(v) * __uint_as_float(u[j]));
-            else if (args.mode == MODE_STORE_F32) ((float*)args.C)[idx] = v;
-            else if (args.mode == MODE_ACCUM_F32) ((float*)args.C)[idx] += v;
-            else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(v);
+            for (int j = 0; j < 16; ++j) prev[j] = j < valid ? cf[(size_t)j * args.ldc] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (j < valid) cf[(size_t)j * args.ldc] = prev[j] + __uint_as_float(r[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j >= valid) break;
+              const float v = __uint_as_float(r[j]);
+              if (SWIGLU) cb[(size_t)j * args.ldc] = __float2bfloat16_rn(silu_f(v) * __uint_as_float(u[j]));
+              else if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
+              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
+            }
           }
         }
       }
@@ -390,13 +417,15 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int 
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splits;   // the splits of one tile share their partials
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWIGLU>, tw, tx, a);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

@@ -15,6 +15,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 #define SAMPLE_THREADS 1024
 #define FIX_ONE 1099511627776.0f  // 2^40
 
@@ -34,6 +36,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
   __shared__ uint32_t sk[32];
   __shared__ int si[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const float* row = logits + (size_t)blockIdx.x * ld;
   uint32_t best = 0u;
   int best_i = 0x7fffffff;
@@ -68,8 +72,7 @@ extern "C" int tl_argmax(const float* logits, int ld, int rows, int V, int* out,
                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return -1;
-  argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, out);
-  return (int)cudaGetLastError();
+  return tl_launch(argmax_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, out);
 }
 
 // --------------------------------------------------------------------------
@@ -179,6 +182,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature, int top_k,
               float top_p, const float* __restrict__ uniform, int* __restrict__ out) {
   __shared__ SampleShared sm;
+  pdl_wait();
+  pdl_launch_dependents();
   const int tid = threadIdx.x;
   RowView rv;
   rv.row = logits + (size_t)blockIdx.x * ld;
@@ -327,7 +332,6 @@ extern "C" int tl_sample(const float* logits, int ld, int rows, int V, float tem
                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0 || !(temperature > 0.0f)) return -1;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p,
-                                                     uniform, out);
-  return (int)cudaGetLastError();
+  return tl_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V,
+                   temperature, top_k, top_p, uniform, out);
 }
