@@ -2,7 +2,7 @@
 returns False for a shape it does not take; the caller then uses the CUDA-core kernel."""
 from __future__ import annotations
 
-from ctypes import c_int, c_longlong, c_void_p
+from ctypes import byref, c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -33,9 +33,13 @@ class GemmBf16:
             self._scratch[key] = torch.cuda.get_device_properties(device).multi_processor_count
         return self._scratch[key]
 
-    def run(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> bool:
-        """out (op)= a @ w.T.  Shapes and types are checked by the caller's generic path
-        when this returns False."""
+    def run(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
+            scaled=None, emit=None) -> bool:
+        """out (op)= a @ w.T.  Returns False for shapes this kernel does not take.
+
+        `scaled`: a `NormCarry` whose `xw` is `a`; outputs are scaled by each row's
+        1/rms from its partial sums.  `emit`: (norm weight, NormCarry) for mode 1: if the
+        kernel can, it fills the carry with the next norm's input and sets `carry.valid`."""
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             return False
         if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
@@ -47,12 +51,23 @@ class GemmBf16:
             raise KernelError(f"gemm: shapes or types do not fit: a {tuple(a.shape)} w {tuple(w.shape)} "
                               f"out {tuple(out.shape)} {out.dtype} mode {mode}")
         sms = self._scratch_for(a.device)
-        st = self.lib.tl_gemm_tc(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
-                                 c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(mode),
-                                 c_int(sms), _stream())
+        emitted = c_int(0)
+        ss_in = scaled.ss if scaled is not None else None
+        nw, carry = emit if emit is not None else (None, None)
+        st = self.lib.tl_gemm_tc(
+            _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
+            c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(sms),
+            _ptr(ss_in), c_int(scaled.tiles if scaled is not None else 0),
+            c_int(scaled.size if scaled is not None else 0),
+            c_float(scaled.eps if scaled is not None else 0.0),
+            _ptr(carry.xw if carry is not None else None), _ptr(nw),
+            c_int(1 if (nw is not None and nw.dtype == torch.float32) else 0),
+            _ptr(carry.ss if carry is not None else None), byref(emitted), _stream())
         if st == -2:
             return False
         _check(st, "gemm_tc")
+        if carry is not None:
+            carry.valid = bool(emitted.value)
         return True
 
     def take_error(self) -> int:

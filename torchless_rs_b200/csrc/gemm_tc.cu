@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "pdl.cuh"
 
@@ -176,7 +177,22 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g));
 struct GemmArgs {
   void* C;
   int ldc, M, N, K, mode, kb_per_split, stages;
+  // Norm folded into the products around it (see the launcher's text).
+  const float* ss_in;       // [M, ss_in_tiles] partial sums of squares of the input rows, or null
+  int ss_in_tiles, norm_h;
+  float eps_in;
+  __nv_bfloat16* xw_out;    // [M, N] the new C times the next norm's weight, or null
+  const void* nw;           // that weight [N]
+  int nw_is_f32;
+  float* ss_out;            // [M, tiles of N] partial sums of squares of the new C
 };
+
+// 1 / sqrt(mean(x^2) + eps) of input row m from the partial sums the producer left.
+__device__ __forceinline__ float row_rinv(const GemmArgs& a, int m) {
+  float ss = 0.0f;
+  for (int t = 0; t < a.ss_in_tiles; ++t) ss += __ldcg(a.ss_in + (size_t)m * a.ss_in_tiles + t);
+  return 1.0f / sqrtf(ss / (float)a.norm_h + a.eps_in);
+}
 
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS)
@@ -281,6 +297,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const int n = n0 + row;
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
     float* red = (float*)smem;   // partial tile [columns][128 rows]; the stages are free by now
+    float* rinv_s = (float*)smem;   // without a split the same place holds the row scales
+    if (ok && splits == 1 && args.ss_in) {
+      for (int c = threadIdx.x; c < BN; c += 128)
+        rinv_s[c] = m0 + c < args.M ? row_rinv(args, m0 + c) : 0.0f;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     if (ok) {
       for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t r[16], u[16];
@@ -308,8 +330,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               if (j >= valid) break;
-              const float v = __uint_as_float(r[j]);
-              if (SWIGLU) cb[(size_t)j * args.ldc] = __float2bfloat16_rn(silu_f(v) * __uint_as_float(u[j]));
+              const float sc = args.ss_in ? rinv_s[c0 + j] : 1.0f;
+              const float v = __uint_as_float(r[j]) * sc;
+              if (SWIGLU) cb[(size_t)j * args.ldc] = __float2bfloat16_rn(silu_f(v) * (__uint_as_float(u[j]) * sc));
               else if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
               else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
             }
@@ -322,22 +345,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   if (splits > 1) {
     cluster_sync_all();   // every block's partial tile is in its shared memory
     if (warp < 4) {
+      pdl_wait();
       const int row = warp * 32 + lane;
       const int n = n0 + row;
       const uint32_t red_s = smem_u32(smem);
       const int cols = min(BN, args.M - m0);
-      if (n < args.N && !*abort_flag) {
-        for (int c = (int)cluster_rank(); c < cols; c += splits) {
-          float v = 0.0f, uu = 0.0f;
-          for (int sp = 0; sp < splits; ++sp) {
-            v += ld_remote_f32(red_s + (uint32_t)(c * TILE_N + row) * 4u, (uint32_t)sp);
-            if (SWIGLU) uu += ld_remote_f32(red_s + (uint32_t)((BN + c) * TILE_N + row) * 4u, (uint32_t)sp);
+      const bool live = n < args.N && !*abort_flag;
+      float* ssw = (float*)(smem + (size_t)stages * STAGE_BYTES) + 64;   // [4 warps][64] after the barriers
+      float* rinv_c = ssw + 256;                                          // [BN] scales of the input rows
+      if (args.ss_in) {   // one scale per token, all tokens at once
+        for (int c = threadIdx.x; c < cols; c += 128) rinv_c[c] = row_rinv(args, m0 + c);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      const int rank = (int)cluster_rank();
+      const bool accum = args.mode == MODE_ACCUM_F32 && !SWIGLU;
+      int my_cols = 0;
+      // columns rank, rank + splits, ... in groups of 8, so that the loads of a group (old C,
+      // partials of every split) are in flight together
+      for (int cb = rank; cb < cols; cb += 8 * splits) {
+        float v[8], uu[8], prev[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int c = cb + q * splits;
+          prev[q] = (accum && live && c < cols) ? ((const float*)args.C)[(size_t)(m0 + c) * args.ldc + n] : 0.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int c = cb + q * splits;
+          v[q] = uu[q] = 0.0f;
+          if (c < cols) {
+            for (int sp = 0; sp < splits; ++sp) {
+              v[q] += ld_remote_f32(red_s + (uint32_t)(c * TILE_N + row) * 4u, (uint32_t)sp);
+              if (SWIGLU) uu[q] += ld_remote_f32(red_s + (uint32_t)((BN + c) * TILE_N + row) * 4u, (uint32_t)sp);
+            }
           }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int c = cb + q * splits;
+          if (c >= cols) break;
+          float val = v[q], up = uu[q];
+          if (args.ss_in) { val *= rinv_c[c]; up *= rinv_c[c]; }
           const size_t idx = (size_t)(m0 + c) * args.ldc + n;
-          if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(v) * uu);
-          else if (args.mode == MODE_STORE_F32) ((float*)args.C)[idx] = v;
-          else if (args.mode == MODE_ACCUM_F32) ((float*)args.C)[idx] += v;
-          else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(v);
+          float sq = 0.0f;
+          if (live) {
+            if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(val) * up);
+            else if (args.mode == MODE_STORE_F32) ((float*)args.C)[idx] = val;
+            else if (accum) {
+              const float cn = prev[q] + val;
+              ((float*)args.C)[idx] = cn;
+              if (args.xw_out) {
+                const float w = args.nw_is_f32 ? ((const float*)args.nw)[n]
+                                               : __bfloat162float(((const __nv_bfloat16*)args.nw)[n]);
+                args.xw_out[(size_t)(m0 + c) * args.N + n] = __float2bfloat16_rn(cn * w);
+                sq = cn * cn;
+              }
+            } else ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(val);
+          }
+          if (args.xw_out) {   // sum of squares of this tile's 128 columns, in a fixed order
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) ssw[warp * 64 + my_cols] = sq;
+          }
+          ++my_cols;
+        }
+      }
+      if (args.xw_out) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if ((int)threadIdx.x < my_cols) {
+          const int c = rank + (int)threadIdx.x * splits;
+          const float t = ((ssw[threadIdx.x] + ssw[64 + threadIdx.x]) + ssw[128 + threadIdx.x]) + ssw[192 + threadIdx.x];
+          args.ss_out[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = t;
         }
       }
     }
@@ -400,11 +478,11 @@ template <int BN, bool SWIGLU>
 static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int splits,
                   size_t smem_budget, cudaStream_t stream) {
   const size_t stage = (size_t)TILE_N * TILE_K * 2 * (SWIGLU ? 2 : 1) + (size_t)BN * TILE_K * 2;
-  int stages = (int)((smem_budget - 1024 - 256) / stage);
+  int stages = (int)((smem_budget - 1024 - 2048) / stage);
   stages = stages > 8 ? 8 : stages;
   if (stages < 2) return -2;
   a.stages = stages;
-  const size_t smem = 1024 + stages * stage + 256;
+  const size_t smem = 1024 + stages * stage + 2048;
   static size_t configured = 0;   // per instantiation
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWIGLU>,
@@ -434,8 +512,18 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int 
 
 // Returns 0, a CUDA error, or -2 when these sizes or alignments are not taken (the
 // caller then uses the CUDA-core kernel).  N counts output columns; in mode 2 W has 2N rows.
+//
+// A norm between two products can be folded into them.  Producer side (mode 1 only): if
+// `xw_out` is given and K is split, the kernel also writes xw_out[m, n] = bf16(C_new[m, n] *
+// nw[n]) and ss_out[m, tile] = the sum of C_new[m, n]^2 over the tile's 128 columns, and
+// sets *emitted = 1; otherwise *emitted = 0 and the caller runs the norm kernel.  Consumer
+// side: with `ss_in` given, X is such an xw and every output is scaled by
+// 1 / sqrt(sum_t ss_in[m, t] / norm_h + eps_in) before the mode's operation.
 extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* C, int ldc, int M,
-                          int N, int K, int mode, int num_sms, cudaStream_t stream) {
+                          int N, int K, int mode, int num_sms, const float* ss_in, int ss_in_tiles,
+                          int norm_h, float eps_in, void* xw_out, const void* nw, int nw_is_f32,
+                          float* ss_out, int* emitted, cudaStream_t stream) {
+  if (emitted) *emitted = 0;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
     return -2;
@@ -447,7 +535,9 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   const int kb_total = (K + TILE_K - 1) / TILE_K;
   // two blocks per SM fit while the token tile is small
   const bool two_per_sm = bn <= 64;
-  const size_t budget = two_per_sm ? 112 * 1024 : 224 * 1024;
+  // small token tiles leave room for the blocks of the next kernel, which fetch their first
+  // weight tiles while this kernel drains
+  const size_t budget = !two_per_sm ? 224 * 1024 : (!swiglu && bn <= 32) ? 80 * 1024 : 112 * 1024;
   const long long slots = (long long)num_sms * (two_per_sm ? 2 : 1);
   int splits = 1;
   if (tiles < slots && two_per_sm) {
@@ -464,6 +554,11 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   GemmArgs a;
   a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
   a.mode = mode; a.kb_per_split = kb_per_split; a.stages = 0;
+  a.ss_in = ss_in; a.ss_in_tiles = ss_in_tiles; a.norm_h = norm_h; a.eps_in = eps_in;
+  const bool emit = xw_out && ss_out && nw && mode == MODE_ACCUM_F32 && splits > 1 && N % 8 == 0;
+  a.xw_out = emit ? (__nv_bfloat16*)xw_out : nullptr;
+  a.nw = nw; a.nw_is_f32 = nw_is_f32; a.ss_out = emit ? ss_out : nullptr;
+  if (emitted) *emitted = emit ? 1 : 0;
 #define DISPATCH(BN_)                                                                      \
   return swiglu ? launch<BN_, true>(tw, tx, a, splits, budget, stream)                    \
                 : launch<BN_, false>(tw, tx, a, splits, budget, stream)

@@ -123,9 +123,15 @@ class DecoderModel:
         T, H = batch.n_tokens, self.spec.hidden_size
         x = ws.get("stream", (T, H), torch.float32)
         rt.ops.embed(batch.tokens, self.embedding, x)
-        for k, i in enumerate(self.spec.order):
+        order = self.spec.order
+        carry = None
+        for k, i in enumerate(order):
             self.mixers[i].bind_cache(self.views[k])
-            self.blocks[i].forward(x, batch)
+            nxt = self.blocks[order[k + 1]] if k + 1 < len(order) else None
+            # the next block takes a prepared norm input only if its mixer can use one
+            next_norm = (nxt.mixer_norm if nxt is not None
+                         and getattr(nxt.mixer, "accepts_carry", False) else None)
+            carry = self.blocks[i].forward(x, batch, carry, next_norm)
         if batch.n_want == 0:
             return None
         xn = ws.get("head_normed", (batch.n_want, H), rt.act_dtype)

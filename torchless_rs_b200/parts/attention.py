@@ -87,9 +87,11 @@ class Attention:
     def bind_cache(self, view) -> None:
         self.cache = view
 
-    def forward(self, xn: torch.Tensor, residual: torch.Tensor, batch) -> None:
+    accepts_carry = True   # `xn` may be a NormCarry; `emit` may ask for the next norm's input
+
+    def forward(self, xn, residual: torch.Tensor, batch, emit=None) -> None:
         rt, ws = self.rt, self.rt.workspace
-        T = xn.shape[0]
+        T = residual.shape[0]
         c = self.cache
         qkv = ws.get("attn_qkv", (T, self.qkv_cols), torch.float32)
         self.matmul(xn, self.w_qkv, qkv, ops.MODE_STORE_F32)
@@ -109,4 +111,4 @@ class Attention:
             rt.ops.attn_generic(q, c.k_pages, c.v_pages, out, batch.token_pos, batch.token_seq,
                                 batch.seq_slot, c.page_table, self.nh, self.nkv, self.hd,
                                 self.window, self.scale)
-        self.matmul(out, self.w_o, residual, ops.MODE_ACCUM_F32)
+        self.matmul(out, self.w_o, residual, ops.MODE_ACCUM_F32, emit=emit)

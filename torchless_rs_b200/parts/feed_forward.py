@@ -48,8 +48,10 @@ class SwiGLU:
                                     self.rt.matrix(weights[f"{p}.up_proj.weight"])], dim=0)
         self.w_down = self.rt.matrix(weights[f"{p}.down_proj.weight"])
 
-    def forward(self, xn: torch.Tensor, residual: torch.Tensor, batch) -> None:
-        T = xn.shape[0]
+    accepts_carry = True   # `xn` may be a NormCarry; `emit` may ask for the next norm's input
+
+    def forward(self, xn, residual: torch.Tensor, batch, emit=None) -> None:
+        T = residual.shape[0]
         act = self.rt.workspace.get("ffn_act", (T, self.inter), self.rt.act_dtype)
         self.matmul(xn, self.w_gate_up, act, ops.MODE_SWIGLU)
-        self.matmul(act, self.w_down, residual, ops.MODE_ACCUM_F32)
+        self.matmul(act, self.w_down, residual, ops.MODE_ACCUM_F32, emit=emit)

@@ -13,6 +13,25 @@ from ..csrc import ops
 from .runtime import Runtime
 
 
+class NormCarry:
+    """The input of a norm that the product before it has already prepared: `xw` = the
+    stream times the norm's weight (bfloat16), `ss` = partial sums of squares of each row
+    of the stream, one per 128 columns.  The product after it scales its outputs by
+    1/rms.  `valid` says whether the last producer filled it."""
+
+    def __init__(self, xw: torch.Tensor, ss: torch.Tensor, size: int, eps: float):
+        self.xw, self.ss, self.size, self.eps = xw, ss, size, eps
+        self.tiles = ss.shape[1]
+        self.valid = False
+
+
+def new_carry(rt: Runtime, name: str, n_tokens: int, size: int, eps: float) -> NormCarry:
+    ws = rt.workspace
+    tiles = (size + 127) // 128
+    return NormCarry(ws.get(f"carry_xw_{name}", (n_tokens, size), torch.bfloat16),
+                     ws.get(f"carry_ss_{name}", (n_tokens, tiles), torch.float32), size, eps)
+
+
 class Matmul:
     def __init__(self, rt: Runtime):
         self.rt = rt
@@ -21,7 +40,16 @@ class Matmul:
             from ..csrc import gemm_bf16
             self.fast = gemm_bf16.GemmBf16.get()
 
-    def __call__(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> None:
-        if self.fast is not None and self.fast.run(a, w, out, mode):
+    def __call__(self, a, w: torch.Tensor, out: torch.Tensor, mode: int, emit=None) -> None:
+        """`a` is an activation tensor or a `NormCarry`.  `emit` = (norm weight, NormCarry)
+        asks the product (mode 1) to prepare the next norm's input if it can."""
+        scaled = a if isinstance(a, NormCarry) else None
+        if scaled is not None:
+            if self.fast is None or not self.fast.run(scaled.xw, w, out, mode, scaled=scaled):
+                raise ops.KernelError("a folded norm reached a product that cannot apply it")
+            return
+        if emit is not None:
+            emit[1].valid = False
+        if self.fast is not None and self.fast.run(a, w, out, mode, emit=emit):
             return
         self.rt.ops.gemm_generic(a, w, out, mode)

@@ -18,6 +18,8 @@ class RMSNorm:
     `load(weights)`, and `__call__(x, out, rows=None)` from the 32-bit stream to an
     activation tensor; `rows` (int32, on the device) picks input rows."""
 
+    foldable = True   # x / rms * w with a plain weight: the products around it can take it over
+
     def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
