@@ -14,8 +14,7 @@ from .ops import KernelError, _check, _need, _ptr, _stream
 
 FAST_HEAD_DIMS = (32, 64, 128)
 MAX_GROUP = 16        # query heads per key/value head that one instruction's rows hold
-import os
-TARGET_BLOCKS = int(os.environ.get('TL_ATTN_BLOCKS', 592))   # 148 SMs x 2 resident blocks x 2 waves
+TARGET_BLOCKS = 592   # 148 SMs x 2 resident blocks x 2 waves
 
 for _hd in FAST_HEAD_DIMS:
     build.register_library(f"attn_bf16_hd{_hd}",

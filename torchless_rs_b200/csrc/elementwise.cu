@@ -30,6 +30,7 @@ extern "C" int TL_NAME(tl_embed)(const int* tokens, const void* table, float* x,
 // act_t (reference: src/kernels/mod.rs:558-568).  `rows` (optional) picks the
 // input rows, so the final norm runs on the wanted rows only.
 // ---------------------------------------------------------------------------
+#define NORM_MAX_PER_THREAD 16
 template <typename W>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const W* __restrict__ w, act_t* __restrict__ y, int H, float eps) {
@@ -38,16 +39,36 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
   pdl_launch_dependents();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+  act_t* yr = y + (size_t)r * H;
+  // the row is read once and kept in registers if it fits, else read a second time
+  const bool fits = H <= (int)blockDim.x * NORM_MAX_PER_THREAD;
+  float keep[NORM_MAX_PER_THREAD];
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = xr[i];
-    ss = fmaf(v, v, ss);
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      keep[j] = i < H ? xr[i] : 0.0f;
+      ss = fmaf(keep[j], keep[j], ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float v = xr[i];
+      ss = fmaf(v, v, ss);
+    }
   }
   ss = block_sum(ss, scratch);
   const float rms = sqrtf(ss / (float)H + eps);
-  act_t* yr = y + (size_t)r * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x)
-    yr[i] = from_f32<act_t>((xr[i] / rms) * to_f32(w[i]));
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_PER_THREAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < H) yr[i] = from_f32<act_t>((keep[j] / rms) * to_f32(w[i]));
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+      yr[i] = from_f32<act_t>((xr[i] / rms) * to_f32(w[i]));
+  }
 }
 
 extern "C" int TL_NAME(tl_rmsnorm)(const float* x, const int* rows, const void* w, int w_is_f32,
@@ -82,46 +103,45 @@ __global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
                                         const int* __restrict__ seq_slot,
                                         const int* __restrict__ page_table, int table_stride,
                                         const float* __restrict__ inv_freq, int style, int nh,
-                                        int nkv, int hd) {
-  // grid (tokens, heads): query heads, then key heads, then value heads
+                                        int nkv, int hd, int heads_per_block) {
+  // grid (tokens, groups of heads); heads count query heads, then key heads, then value heads
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int t = blockIdx.x;
   const int pos = token_pos[t];
   const int half = hd >> 1;
-  const float* row = qkv + (size_t)t * ld + (size_t)h * hd;
-  size_t page_base = 0;
-  bool page_ok = true;
-  if (h >= nh) {
-    const int slot = seq_slot[token_seq[t]];
-    const int page = page_table[(size_t)slot * table_stride + pos / TL_PAGE];
-    page_ok = page >= 0;
-    const int kvh = h - nh < nkv ? h - nh : h - nh - nkv;
-    page_base = ((size_t)(page_ok ? page : 0) * nkv + kvh) * (size_t)(TL_PAGE * hd);
-  }
-  if (!page_ok) return;
-  if (h < nh + nkv) {
-    act_t* dst = h < nh ? q_out + (size_t)t * nh * hd + (size_t)h * hd
-                        : k_pages + page_base + (size_t)(pos % TL_PAGE) * hd;
-    const float fpos = (float)pos;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-      const int d0 = style == 0 ? i : 2 * i;
-      const int d1 = style == 0 ? i + half : 2 * i + 1;
-      const float a = row[d0], b = row[d1];
-      float ra = a, rb = b;
-      if (inv_freq) {
-        float s, c;
-        sincosf(fpos * inv_freq[i], &s, &c);
-        ra = a * c - b * s;
-        rb = a * s + b * c;
+  const int total_heads = nh + (k_pages ? 2 * nkv : 0);
+  const int h_end = min((int)(blockIdx.y + 1) * heads_per_block, total_heads);
+  int page = -1;
+  if (k_pages) page = page_table[(size_t)seq_slot[token_seq[t]] * table_stride + pos / TL_PAGE];
+  const float fpos = (float)pos;
+  for (int h = blockIdx.y * heads_per_block; h < h_end; ++h) {
+    const float* row = qkv + (size_t)t * ld + (size_t)h * hd;
+    if (h >= nh && page < 0) continue;
+    const int kvh = h < nh ? 0 : (h - nh < nkv ? h - nh : h - nh - nkv);
+    const size_t page_base = ((size_t)(page < 0 ? 0 : page) * nkv + kvh) * (size_t)(TL_PAGE * hd);
+    if (h < nh + nkv) {
+      act_t* dst = h < nh ? q_out + (size_t)t * nh * hd + (size_t)h * hd
+                          : k_pages + page_base + (size_t)(pos % TL_PAGE) * hd;
+      for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const int d0 = style == 0 ? i : 2 * i;
+        const int d1 = style == 0 ? i + half : 2 * i + 1;
+        const float a = row[d0], b = row[d1];
+        float ra = a, rb = b;
+        if (inv_freq) {
+          float s, c;
+          sincosf(fpos * inv_freq[i], &s, &c);
+          ra = a * c - b * s;
+          rb = a * s + b * c;
+        }
+        dst[d0] = from_f32<act_t>(ra);
+        dst[d1] = from_f32<act_t>(rb);
       }
-      dst[d0] = from_f32<act_t>(ra);
-      dst[d1] = from_f32<act_t>(rb);
+    } else {
+      // values lie transposed in a page: [hd][TL_PAGE]
+      act_t* dst = v_pages + page_base + (pos % TL_PAGE);
+      for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[(size_t)d * TL_PAGE] = from_f32<act_t>(row[d]);
     }
-  } else {
-    // values lie transposed in a page: [hd][TL_PAGE]
-    act_t* dst = v_pages + page_base + (pos % TL_PAGE);
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[(size_t)d * TL_PAGE] = from_f32<act_t>(row[d]);
   }
 }
 
@@ -134,11 +154,14 @@ extern "C" int TL_NAME(tl_rope_cache_write)(const float* qkv, int ld, void* q_ou
   if (T <= 0) return 0;
   if (hd & 1) return TL_ERR_BAD_ARG;
   const int heads = nh + (k_pages ? 2 * nkv : 0);
-  if (heads > 65535) return TL_ERR_UNSUPPORTED;
-  dim3 grid(T, heads);
+  // few tokens: one head per block, for parallelism; many tokens: fewer, larger blocks
+  const int per_block = T >= 256 ? 8 : 1;
+  const int groups = (heads + per_block - 1) / per_block;
+  if (groups > 65535) return TL_ERR_UNSUPPORTED;
+  dim3 grid(T, groups);
   return tl_launch(rope_cache_write_kernel, grid, dim3(64), 0, stream, qkv, ld, (act_t*)q_out,
                    (act_t*)k_pages, (act_t*)v_pages, token_pos, token_seq, seq_slot, page_table,
-                   table_stride, inv_freq, style, nh, nkv, hd);
+                   table_stride, inv_freq, style, nh, nkv, hd, per_block);
 }
 
 // ---------------------------------------------------------------------------

@@ -1,0 +1,104 @@
+"""Single-kernel runs for timing and profiling.
+
+    python -m torchless_rs_b200.measure gemm M N K MODE [--iters I]
+    python -m torchless_rs_b200.measure attn-decode BATCH CONTEXT [--iters I]
+    python -m torchless_rs_b200.measure attn-prefill TOKENS [--iters I]
+
+Each prints the mean device time per launch (CUDA events, after warm-up; the weights
+or the cache are larger than the L2 cache or rotated so that they come from HBM) and
+the bandwidth or arithmetic rate that this time means.  Sizes other than the ones
+given default to those of Mistral 7B (32 heads, 8 key/value heads, head size 128).
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+
+def _time(fn, iters: int) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters   # microseconds
+
+
+def gemm(M: int, N: int, K: int, mode: int, iters: int) -> None:
+    from .csrc.gemm_bf16 import GemmBf16
+    g = GemmBf16.get()
+    rows = 2 * N if mode == 2 else N
+    copies = max(2, int(400e6 // (rows * K * 2)) + 1)     # rotate weights: more than the L2 holds
+    ws = [torch.randn((rows, K), device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    x = torch.randn((M, K), device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros((M, N), device="cuda", dtype=torch.float32 if mode in (0, 1) else torch.bfloat16)
+    state = {"i": 0}
+
+    def run():
+        assert g.run(x, ws[state["i"] % copies], out, mode), "shape not taken by the tensor-core kernel"
+        state["i"] += 1
+    us = _time(run, iters)
+    print(f"gemm M={M} N={N} K={K} mode={mode}: {us:.2f} us, "
+          f"{rows * K * 2 / us / 1e3:.0f} GB/s of weights, {2.0 * M * rows * K / us / 1e6:.1f} TFLOP/s, "
+          f"error word {g.take_error()}")
+
+
+def _paged(B: int, ctx: int, nkv: int, hd: int):
+    pages = (ctx + 63) // 64
+    kp = torch.randn((B * pages, nkv, 64, hd), device="cuda", dtype=torch.bfloat16)
+    vp = torch.randn((B * pages, nkv, hd, 64), device="cuda", dtype=torch.bfloat16)
+    table = torch.arange(B * pages, dtype=torch.int32, device="cuda").view(B, pages)
+    slot = torch.arange(B, dtype=torch.int32, device="cuda")
+    return kp, vp, table, slot
+
+
+def attn_decode(B: int, ctx: int, iters: int, nh=32, nkv=8, hd=128) -> None:
+    from .csrc.attention_bf16 import AttentionBf16, decode_splits
+    from .parts.runtime import Workspace
+    att, ws = AttentionBf16.get(hd), Workspace(torch.device("cuda"))
+    kp, vp, table, slot = _paged(B, ctx, nkv, hd)
+    lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    q = torch.randn((B, nh * hd), device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    n = decode_splits(B, nkv, ctx, None)
+    us = _time(lambda: att.decode(q, kp, vp, out, lens, slot, table, nh, nkv, None,
+                                  1 / math.sqrt(hd), n, ws), iters)
+    byts = 2.0 * B * ctx * nkv * hd * 2
+    print(f"attn-decode B={B} context={ctx} splits={n}: {us:.2f} us (both kernels), {byts / us / 1e3:.0f} GB/s of cache")
+
+
+def attn_prefill(T: int, iters: int, nh=32, nkv=8, hd=128) -> None:
+    from .csrc.attention_bf16 import AttentionBf16
+    att = AttentionBf16.get(hd)
+    kp, vp, table, slot = _paged(1, T, nkv, hd)
+    start = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+    lens = torch.tensor([T], dtype=torch.int32, device="cuda")
+    q = torch.randn((T, nh * hd), device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    us = _time(lambda: att.prefill(q, kp, vp, out, start, lens, slot, table, 1, T, nh, nkv, None,
+                                   1 / math.sqrt(hd)), iters)
+    print(f"attn-prefill tokens={T}: {us:.2f} us, {2.0 * nh * hd * T * T / us / 1e6:.1f} TFLOP/s (causal half counted)")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill"])
+    ap.add_argument("sizes", type=int, nargs="+")
+    ap.add_argument("--iters", type=int, default=50)
+    a = ap.parse_args()
+    if a.what == "gemm":
+        gemm(*a.sizes[:4], a.iters)
+    elif a.what == "attn-decode":
+        attn_decode(a.sizes[0], a.sizes[1], a.iters)
+    else:
+        attn_prefill(a.sizes[0], a.iters)
+
+
+if __name__ == "__main__":
+    main()
