@@ -501,7 +501,8 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int 
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splits;   // the splits of one tile share their partials
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  static const int pdl_on = getenv("TL_NO_PDL") ? 0 : 1;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_on;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWIGLU>, tw, tx, a);
@@ -529,7 +530,8 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
     return -2;
   if (mode < 0 || mode > 3) return -1;
   const bool swiglu = mode == MODE_SWIGLU;
-  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (M > 128 && getenv("TL_GEMM_BIG_BN")) bn = atoi(getenv("TL_GEMM_BIG_BN"));
   const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = (M + bn - 1) / bn;
   const long long tiles = (long long)n_tiles * m_tiles;
   const int kb_total = (K + TILE_K - 1) / TILE_K;
@@ -537,14 +539,17 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   const bool two_per_sm = bn <= 64;
   // small token tiles leave room for the blocks of the next kernel, which fetch their first
   // weight tiles while this kernel drains
-  const size_t budget = !two_per_sm ? 224 * 1024 : (!swiglu && bn <= 32) ? 80 * 1024 : 112 * 1024;
+  const size_t big_budget = getenv("TL_GEMM_BIG_KB") ? (size_t)atoi(getenv("TL_GEMM_BIG_KB")) * 1024 : 224 * 1024;
+  const size_t budget = !two_per_sm ? big_budget : (!swiglu && bn <= 32) ? 80 * 1024 : 112 * 1024;
   const long long slots = (long long)num_sms * (two_per_sm ? 2 : 1);
   int splits = 1;
   if (tiles < slots && two_per_sm) {
-    splits = (int)(slots / tiles);
-    if (splits > kb_total / 2) splits = kb_total / 2;
-    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
-    if (splits < 1) splits = 1;
+    // a power of two (clusters of 3, 5, 6 or 7 blocks do not tile the GPCs evenly, and a
+    // cluster that has to wait for a second wave doubles the kernel's time), as large as
+    // keeps every block resident at once
+    while (splits * 2 <= MAX_SPLITS && tiles * splits * 2 <= slots && splits * 2 <= kb_total / 2)
+      splits *= 2;
+    if (getenv("TL_GEMM_SPLITS")) splits = atoi(getenv("TL_GEMM_SPLITS"));
   }
   int kb_per_split = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split

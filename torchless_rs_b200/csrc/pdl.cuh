@@ -1,6 +1,7 @@
 // Launch helper and device calls for programmatic dependent launch, shared by all kernels.
 #pragma once
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 // ---------------------------------------------------------------------------
 // Programmatic dependent launch.  Every kernel of this package is launched with the
@@ -25,7 +26,8 @@ static inline int tl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  static const int pdl_on = getenv("TL_NO_PDL") ? 0 : 1;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_on;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);

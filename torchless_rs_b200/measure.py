@@ -18,16 +18,25 @@ import torch
 
 
 def _time(fn, iters: int) -> float:
+    """Mean microseconds per call.  The calls are recorded into one CUDA graph and the graph
+    is replayed, so the host's launch cost (some ten microseconds per call from Python) does
+    not bound what is measured."""
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(iters):
-        fn()
+    for _ in range(3):
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e3 / iters   # microseconds
+    return e0.elapsed_time(e1) * 1e3 / (3 * iters)   # microseconds
 
 
 def gemm(M: int, N: int, K: int, mode: int, iters: int) -> None:
