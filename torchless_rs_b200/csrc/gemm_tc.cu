@@ -427,6 +427,157 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------
+// The persistent kernel for many tokens (no K split).  One block per SM walks over output
+// tiles; the accumulator is double-buffered in tensor memory, so the four epilogue warps
+// write tile i while the issuing thread already runs the instructions of tile i + 1, and
+// the TMA ring runs on across tile borders.  Tiles are numbered with the token tile
+// fastest, so that blocks running at the same time share weight tiles in L2.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w,
+                          const __grid_constant__ CUtensorMap tm_x, const GemmArgs args,
+                          int m_tiles, int total_tiles) {
+  constexpr uint32_t A_BYTES = TILE_N * TILE_K * 2;
+  constexpr uint32_t B_BYTES = BN * TILE_K * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
+  constexpr uint32_t ACC_COLS = BN * (SWIGLU ? 2 : 1);
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;   // two accumulators; 256 or 512 columns
+  static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "two accumulators must fill a power of two");
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(TILE_N >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stages = args.stages;
+  uint64_t* full_bar = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + 8;
+  uint64_t* acc_full = empty_bar + 8;    // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_total = (args.K + TILE_K - 1) / TILE_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) pdl_launch_dependents();
+
+  if (warp == 4 && lane == 0) {
+    // ---- TMA producer: one ring of stages across all tiles of this block
+    bool waited = false;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int n0 = (tile / m_tiles) * TILE_N, m0 = (tile % m_tiles) * BN;
+      for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) { tile = total_tiles; break; }
+        uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        const int k = kb * TILE_K;
+        tma_load_2d(st, &tm_w, &full_bar[s], k, n0);
+        if (SWIGLU) tma_load_2d(st + A_BYTES, &tm_w, &full_bar[s], k, args.N + n0);
+        if (!waited) { pdl_wait(); waited = true; }   // weights first, activations after the wait
+        tma_load_2d(st + A_BYTES * (SWIGLU ? 2 : 1), &tm_x, &full_bar[s], k, m0);
+      }
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ---- MMA issuer
+    uint32_t it = 0, local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      const uint32_t buf = local & 1u;
+      ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1u) ^ 1u, abort_flag, 4);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + buf * ACC_COLS;
+      for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1u;
+        ok = mbar_wait(&full_bar[s], ph, abort_flag, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const uint64_t da = smem_desc_k128(sa);
+        const uint64_t da2 = smem_desc_k128(sa + A_BYTES);
+        const uint64_t db = smem_desc_k128(sa + A_BYTES * (SWIGLU ? 2 : 1));
+#pragma unroll
+        for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+          const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+          const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);
+          umma_bf16(acc, da + adv, db + adv, IDESC, accum);
+          if (SWIGLU) umma_bf16(acc + BN, da2 + adv, db + adv, IDESC, accum);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(&acc_full[buf]);
+    }
+  } else if (warp < 4) {
+    // ---- epilogue: thread = one weight row = one column of C
+    pdl_wait();
+    const int row = warp * 32 + lane;
+    uint32_t local = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+      const int n0 = (tile / m_tiles) * TILE_N, m0 = (tile % m_tiles) * BN;
+      const int n = n0 + row;
+      const uint32_t buf = local & 1u;
+      if (!mbar_wait(&acc_full[buf], (local >> 1) & 1u, abort_flag, 3)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * ACC_COLS;
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16], u[16];
+        tmem_ld16(taddr + c0, r);
+        if (SWIGLU) tmem_ld16(taddr + BN + c0, u);
+        tmem_ld_wait();
+        if (n < args.N) {
+          float* cf = (float*)args.C + (size_t)(m0 + c0) * args.ldc + n;
+          __nv_bfloat16* cb = (__nv_bfloat16*)args.C + (size_t)(m0 + c0) * args.ldc + n;
+          const int valid = args.M - (m0 + c0);
+          if (args.mode == MODE_ACCUM_F32) {
+            float prev[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) prev[j] = j < valid ? cf[(size_t)j * args.ldc] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (j < valid) cf[(size_t)j * args.ldc] = prev[j] + __uint_as_float(r[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j >= valid) break;
+              const float v = __uint_as_float(r[j]);
+              if (SWIGLU) cb[(size_t)j * args.ldc] = __float2bfloat16_rn(silu_f(v) * __uint_as_float(u[j]));
+              else if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
+              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);   // 128 arrivals free the accumulator for tile i + 2
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
 // Host side: tensor maps (cached), tile and split choice, launch.
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -509,6 +660,39 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int 
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
+template <int BN, bool SWIGLU>
+static int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int num_sms,
+                             cudaStream_t stream) {
+  const size_t stage = (size_t)TILE_N * TILE_K * 2 * (SWIGLU ? 2 : 1) + (size_t)BN * TILE_K * 2;
+  int stages = (int)((224 * 1024 - 1024 - 2048) / stage);
+  stages = stages > 8 ? 8 : stages;
+  if (stages < 2) return -2;
+  a.stages = stages;
+  const size_t smem = 1024 + stages * stage + 2048;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, SWIGLU>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  const int m_tiles = (a.M + BN - 1) / BN;
+  const int total = m_tiles * ((a.N + TILE_N - 1) / TILE_N);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(total < num_sms ? total : num_sms);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  static const int pdl_on = getenv("TL_NO_PDL") ? 0 : 1;
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_on;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_persistent_kernel<BN, SWIGLU>, tw, tx, a, m_tiles, total);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
 #define MAX_SPLITS 8   // portable cluster size
 
 // Returns 0, a CUDA error, or -2 when these sizes or alignments are not taken (the
@@ -553,6 +737,10 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   }
   int kb_per_split = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
+  // many tokens: the persistent kernel with two accumulators (token tile 256, or 128 with
+  // the SiLU-gate's two accumulators per tile)
+  const bool persistent = M > 128 && !ss_in && !getenv("TL_GEMM_NO_PERSISTENT");
+  if (persistent) bn = swiglu ? 128 : 256;
   CUtensorMap tw, tx;
   if (!make_map(&tw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, TILE_N)) return -2;
   if (!make_map(&tx, X, M, K, ldx, bn)) return -2;
@@ -564,6 +752,9 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   a.xw_out = emit ? (__nv_bfloat16*)xw_out : nullptr;
   a.nw = nw; a.nw_is_f32 = nw_is_f32; a.ss_out = emit ? ss_out : nullptr;
   if (emitted) *emitted = emit ? 1 : 0;
+  if (persistent)
+    return swiglu ? launch_persistent<128, true>(tw, tx, a, num_sms, stream)
+                  : launch_persistent<256, false>(tw, tx, a, num_sms, stream);
 #define DISPATCH(BN_)                                                                      \
   return swiglu ? launch<BN_, true>(tw, tx, a, splits, budget, stream)                    \
                 : launch<BN_, false>(tw, tx, a, splits, budget, stream)
