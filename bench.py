@@ -265,6 +265,7 @@ def main() -> int:
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
             "sliding_window": cfg["sliding_window"], "rope_theta": cfg["rope_theta"],
+            "rms_norm_eps": cfg["rms_norm_eps"],
             "global_batch": B, "seq_len": CONTEXT, "mean_context": mean_ctx,
             "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
             "l2": "inputs_exceed_l2", "peaks": peaks["source"],

@@ -11,7 +11,7 @@ from tiny import CONFIGS, random_tokens
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "C", "D"]
+NAMES = ["A", "B", "C", "D", "E"]
 
 
 @pytest.fixture(scope="module", params=[(n, d) for n in NAMES for d in DTYPES],

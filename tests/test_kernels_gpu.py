@@ -345,3 +345,45 @@ def test_attention_prefill_bf16(nh, nkv, hd, window):
             tkn, pos = starts[b] + i, lens[b] - new[b] + i
             ref = attention_reference(qc[tkn], pc.k[b], pc.v[b], pos, window, scale)
             assert torch.allclose(got[tkn], ref, **_attn_tol(dtype)), f"seq {b} pos {pos}"
+
+
+@pytest.mark.parametrize("kernel", ["prefill_bf16", "generic_bf16", "generic_f32"])
+def test_attention_far_key_stands_out_in_every_kernel(kernel):
+    """The same idea as for the decode kernel, for the kernels that take many queries: one
+    key far back matches the last queries strongly; with a window it sits on the window's
+    first and last visible place and one place outside it."""
+    from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
+    dtype = torch.float32 if kernel.endswith("f32") else torch.bfloat16
+    nh, nkv, hd, n = 4, 2, 128 if kernel == "prefill_bf16" else 48, 300
+    scale = 1 / math.sqrt(hd)
+    for window in (None, 100):
+        last = n - 1
+        lo = 0 if window is None else last - window + 1
+        for hot in (lo - 1, lo, lo + 1, 191, 192, last - 1, last):
+            if hot < 0:
+                continue
+            pc = Paged([n], nkv, hd, dtype, 77)
+            q = _rand((n, nh * hd), dtype, 78)
+            qh = q.view(n, nh, hd).float().cpu()
+            k_dense = pc.k[0].clone()
+            for kvh in range(nkv):      # key `hot` points along the last query's mean over its heads
+                qm = qh[last, kvh * (nh // nkv):(kvh + 1) * (nh // nkv)].mean(0)
+                k_dense[hot, kvh] = (qm * 4).to(dtype)
+            page = int(pc.table[pc.slots[0], hot // PAGE])
+            pc.k_pages[page, :, hot % PAGE, :] = k_dense[hot].to(DEV)
+            pc.k[0] = k_dense
+            out = torch.empty((n, nh * hd), dtype=dtype, device=DEV)
+            pos = torch.arange(n, dtype=torch.int32, device=DEV)
+            seq = torch.zeros(n, dtype=torch.int32, device=DEV)
+            if kernel == "prefill_bf16":
+                AttentionBf16.get(hd).prefill(
+                    q, pc.k_pages, pc.v_pages, out, torch.tensor([0, n], dtype=torch.int32, device=DEV),
+                    torch.tensor([n], dtype=torch.int32, device=DEV), pc.seq_slot, pc.table, 1, n, nh, nkv,
+                    window, scale)
+            else:
+                _ops(dtype).attn_generic(q, pc.k_pages, pc.v_pages, out, pos, seq, pc.seq_slot, pc.table,
+                                         nh, nkv, hd, window, scale)
+            got = out.cpu().double().view(n, nh, hd)
+            for p_ in (last, last - 1, max(hot, 0)):     # rows that see the hot key, or just miss it
+                ref = attention_reference(q.cpu().view(n, nh, hd)[p_], pc.k[0], pc.v[0], p_, window, scale)
+                assert torch.allclose(got[p_], ref, **_attn_tol(dtype)), f"{kernel} window {window} hot {hot} row {p_}"

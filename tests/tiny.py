@@ -42,7 +42,14 @@ TINY_D = {
     "rope_theta": 10000.0, "sliding_window": 40, "rms_norm_eps": 1e-5,
     "tie_word_embeddings": False, "max_position_embeddings": 4096,
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+TINY_E = {   # a width and an intermediate size that are no multiples of 8, an odd vocabulary
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 84, "num_attention_heads": 3,
+    "num_key_value_heads": 3, "head_dim": 32, "intermediate_size": 100, "vocab_size": 259,
+    "rope_theta": 10000.0, "sliding_window": None, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_model_dir(cfg: dict, seed: int, dtype=torch.bfloat16, where: str | None = None) -> str:
