@@ -219,9 +219,11 @@ def test_rope_cache_write(dtype, style):
     assert int((kp != 0).any(-1).sum()) <= T * nkv
 
 
+@pytest.mark.parametrize("use_tma", [True, False])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, None), (8, 2, 128, 100), (4, 4, 64, 33),
-                                               (12, 1, 32, None), (32, 8, 128, 4096), (10, 5, 64, 64)])
-def test_attention_decode_bf16(nh, nkv, hd, window):
+                                               (12, 1, 32, None), (32, 8, 128, 4096), (10, 5, 64, 64),
+                                               (12, 1, 128, 70)])
+def test_attention_decode_bf16(nh, nkv, hd, window, use_tma):
     """Split-KV decode kernel: lengths around the 32-key groups and page borders, and
     every split count from one to more than there are groups."""
     from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
@@ -240,14 +242,16 @@ def test_attention_decode_bf16(nh, nkv, hd, window):
     for n_splits in (1, 2, 3, 7, 40):
         out = torch.full((B, nh * hd), float("nan"), dtype=dtype, device=DEV)
         att.decode(q, pc.k_pages, pc.v_pages, out, seq_len, pc.seq_slot, pc.table, nh, nkv, window,
-                   scale, n_splits, ws)
+                   scale, n_splits, ws, use_tma=use_tma)
         got = out.cpu().double().view(B, nh, hd)
         for b in range(B):
             assert torch.allclose(got[b], refs[b], **_attn_tol(dtype)), \
                 f"splits {n_splits} seq {b} (len {lens[b]})"
+    assert att.take_error() == 0
 
 
-def test_attention_decode_far_key_stands_out():
+@pytest.mark.parametrize("use_tma", [True, False])
+def test_attention_decode_far_key_stands_out(use_tma):
     """Random keys give near-uniform weights, which would hide a key that is skipped
     or read from the wrong page.  Here one far key matches the query strongly, so the
     output must be that key's value; its place runs over group, page and window edges."""
@@ -275,7 +279,7 @@ def test_attention_decode_far_key_stands_out():
             out = torch.empty((1, nh * hd), dtype=dtype, device=DEV)
             scale = 1 / math.sqrt(hd)
             att.decode(q, pc.k_pages, pc.v_pages, out, seq_len, pc.seq_slot, pc.table, nh, nkv,
-                       window, scale, 5, ws)
+                       window, scale, 5, ws, use_tma=use_tma)
             ref = attention_reference(q.cpu().view(nh, hd), pc.k[0], pc.v[0], n - 1, window, scale)
             assert torch.allclose(out.cpu().double().view(nh, hd), ref, rtol=2e-2, atol=2e-2), \
                 f"window {window} hot key {hot}"

@@ -14,11 +14,12 @@ from .ops import KernelError, _check, _need, _ptr, _stream
 
 FAST_HEAD_DIMS = (32, 64, 128)
 MAX_GROUP = 16        # query heads per key/value head that one instruction's rows hold
-TARGET_BLOCKS = 592   # 148 SMs x 2 resident blocks x 2 waves
+TARGET_BLOCKS = 296   # 148 SMs x 2 resident blocks: one full wave measured best
 
 for _hd in FAST_HEAD_DIMS:
     build.register_library(f"attn_bf16_hd{_hd}",
-                           ("attention_decode_bf16.cu", "attention_prefill_bf16.cu"),
+                           ("attention_decode_bf16.cu", "attention_prefill_bf16.cu") +
+                           (("attention_decode_tma.cu",) if _hd % 64 == 0 else ()),
                            (f"-DHEAD_DIM={_hd}",))
     # the same kernels with a fixed scratch array inside the library, for callers that must
     # not allocate (see attention_decode_noalloc.h); nothing in this package loads it
@@ -55,9 +56,19 @@ class AttentionBf16:
             self._scratch.restype = c_longlong
             self._prefill = getattr(self.lib, f"tl_attn_prefill_hd{head_dim}")
             self._prefill.restype = c_int
+            self._decode_tma = None
+            if head_dim % 64 == 0:
+                self._decode_tma = getattr(self.lib, f"tl_attn_decode_tma_hd{head_dim}")
+                self._decode_tma.restype = c_int
+                self._tma_error = getattr(self.lib, f"tl_attn_tma_take_error_hd{head_dim}")
+                self._tma_error.restype = c_int
+
+    def take_error(self) -> int:
+        """Nonzero if a TMA kernel gave up on a bounded wait since the last call (synchronises)."""
+        return int(self._tma_error()) if getattr(self, "_decode_tma", None) is not None else 0
 
     def decode(self, q, k_pages, v_pages, out, seq_len, seq_slot, page_table, nh, nkv, window,
-               scale, n_splits, workspace) -> None:
+               scale, n_splits, workspace, use_tma: bool = True) -> None:
         """One new token per sequence; `q` and `out` are [sequences, nh * head_dim]."""
         if self.lib is None:
             raise KernelError(f"no tensor-core decode attention for head size {self.head_dim}")
@@ -66,6 +77,14 @@ class AttentionBf16:
         B = q.shape[0]
         floats = self._scratch(c_int(B), c_int(nh), c_int(n_splits))
         part = workspace.get("attn_decode_partials", (floats,), torch.float32)
+        if self._decode_tma is not None and use_tma:
+            st = self._decode_tma(_ptr(q), _ptr(k_pages), _ptr(v_pages), c_longlong(k_pages.shape[0]),
+                                  _ptr(out), _ptr(part), _ptr(seq_len), _ptr(seq_slot), _ptr(page_table),
+                                  c_int(page_table.stride(0)), c_int(B), c_int(nh), c_int(nkv),
+                                  c_int(window or 0), c_float(scale), c_int(n_splits), _stream())
+            if st != -2:
+                _check(st, "attn_decode_tma")
+                return
         _check(self._decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(part),
                             _ptr(seq_len), _ptr(seq_slot), _ptr(page_table),
                             c_int(page_table.stride(0)), c_int(B), c_int(nh), c_int(nkv),

@@ -1,0 +1,389 @@
+// Decode attention of the bfloat16 path with the cache pages brought in by TMA.
+//
+// Same arithmetic and the same partial results as attention_decode_bf16.cu (and the same
+// second kernel merges the splits), but keys and values do not pass through registers on
+// their way from HBM: a block walks over the pages of its share of a sequence, one
+// thread requests each page's K slab [64 keys x HEAD_DIM] and transposed V slab
+// [HEAD_DIM x 64 keys] of this kv head as 128-byte-swizzled tiles, three pages ahead of
+// the four warps that consume them.  Each warp takes 16 keys of a page.  The fragments of
+// mma.m16n8k16 are read from shared memory with the same freedom as before: contraction
+// slots are mapped to whatever dimensions or keys a 16-byte (K) or 8-byte (V) read
+// delivers, identically for both operands.  Head sizes 64 and 128.
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the block records a code in
+// tl_attn_tma_error and stops.
+#include <cuda.h>
+
+#include "attention_bf16_common.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#define TD_WARPS 4
+#define TD_STAGES 3
+#define K_SUB (HEAD_DIM / 64)                       // 64-column boxes of a K slab
+#define K_BYTES (PAGE * HEAD_DIM * 2)
+#define V_BYTES (HEAD_DIM * PAGE * 2)
+#define TD_STAGE_BYTES (K_BYTES + V_BYTES)
+#define TD_WAIT_LIMIT (1u << 22)
+#define PART_STRIDE (HEAD_DIM + 2)
+
+__device__ int tl_attn_tma_error = 0;
+
+__device__ __forceinline__ uint32_t td_smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void td_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(td_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void td_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(td_smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void td_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(td_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool td_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                             int code) {
+  for (uint32_t i = 0; i < TD_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(td_smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = code;
+  atomicCAS(&tl_attn_tma_error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void td_tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
+                                               int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4}], [%2];"
+      :
+      : "r"(td_smem_u32(dst)), "l"(map), "r"(td_smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+
+template <bool HI>
+__global__ void __launch_bounds__(TD_WARPS * 32, 2)
+FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                           const __nv_bfloat16* __restrict__ q, float* __restrict__ part,
+                           const int* __restrict__ seq_len, const int* __restrict__ seq_slot,
+                           const int* __restrict__ page_table, int table_stride, int nh, int nkv,
+                           int window, float scale_log2, int n_splits) {
+  extern __shared__ uint8_t td_smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)td_smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + TD_STAGES * TD_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + TD_STAGES;
+  volatile int* abort_flag = (volatile int*)(empty_bar + TD_STAGES);
+  // the merge of the four warps reuses the first stage after the loop
+  float* sm_o = (float*)smem;                                   // [warps][16][HEAD_DIM]
+  float* sm_m = sm_o + TD_WARPS * 16 * HEAD_DIM;                // [warps][16]
+  float* sm_l = sm_m + TD_WARPS * 16;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int G = nh / nkv;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TD_STAGES; ++s) { td_mbar_init(&full_bar[s], 1); td_mbar_init(&empty_bar[s], TD_WARPS); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();
+  pdl_launch_dependents();
+
+  const int len = seq_len[b];
+  const int lo = (window > 0 && len - window > 0) ? len - window : 0;
+  const int* table = page_table + (size_t)seq_slot[b] * table_stride;
+  const int first_page = lo / PAGE, last_page = (len - 1) / PAGE;
+  const int per = (last_page - first_page + 1 + n_splits - 1) / n_splits;
+  const int ps = first_page + split * per;
+  const int n_pg = max(0, min(ps + per, last_page + 1) - ps);
+
+  // one thread requests pages; `issue(i)` brings page ps + i into stage i % TD_STAGES
+  auto issue = [&](int i) -> bool {
+    const int s = i % TD_STAGES;
+    if (!td_mbar_wait(&empty_bar[s], ((uint32_t)(i / TD_STAGES) & 1u) ^ 1u, abort_flag, 1)) return false;
+    const int slab = table[ps + i] * nkv + kvh;
+    uint8_t* st = smem + (size_t)s * TD_STAGE_BYTES;
+    td_mbar_expect_tx(&full_bar[s], TD_STAGE_BYTES);
+#pragma unroll
+    for (int sub = 0; sub < K_SUB; ++sub)
+      td_tma_load_2d(st + sub * (PAGE * 128), &tm_k, &full_bar[s], sub * 64, slab * PAGE);
+    td_tma_load_2d(st + K_BYTES, &tm_v, &full_bar[s], 0, slab * HEAD_DIM);
+    return true;
+  };
+  if (threadIdx.x == 0)
+    for (int i = 0; i < TD_STAGES - 1 && i < n_pg; ++i) issue(i);
+
+  // query fragments: rows are the query heads of this kv head
+  uint32_t qa[NCHUNK][4], qb[NCHUNK][4];
+  {
+    const __nv_bfloat16* qrow = q + (size_t)b * nh * HEAD_DIM + (size_t)(kvh * G) * HEAD_DIM;
+#pragma unroll
+    for (int j = 0; j < NCHUNK; ++j) {
+      uint4 va = make_uint4(0, 0, 0, 0), vb = make_uint4(0, 0, 0, 0);
+      if (g < G) va = ldg16(qrow + (size_t)g * HEAD_DIM + (4 * j + t) * 8);
+      if (HI && g + 8 < G) vb = ldg16(qrow + (size_t)(g + 8) * HEAD_DIM + (4 * j + t) * 8);
+      qa[j][0] = va.x; qa[j][1] = va.y; qa[j][2] = va.z; qa[j][3] = va.w;
+      qb[j][0] = vb.x; qb[j][1] = vb.y; qb[j][2] = vb.z; qb[j][3] = vb.w;
+    }
+  }
+  float o[NDT][4];
+#pragma unroll
+  for (int i = 0; i < NDT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+
+  for (int i = 0; i < n_pg; ++i) {
+    if (threadIdx.x == 0 && i + TD_STAGES - 1 < n_pg) issue(i + TD_STAGES - 1);
+    __syncwarp();
+    const int s = i % TD_STAGES;
+    if (!td_mbar_wait(&full_bar[s], (uint32_t)(i / TD_STAGES) & 1u, abort_flag, 2)) break;
+    const uint32_t kb = td_smem_u32(smem + (size_t)s * TD_STAGE_BYTES);
+    const uint32_t vb_ = kb + K_BYTES;
+    const int key0 = (ps + i) * PAGE + 16 * warp;   // first of this warp's 16 keys
+    // ---- scores: 2 tiles of 8 keys; column c of tile jt is key 4*(c>>1) + 2*jt + (c&1)
+    float sc[2][4];
+#pragma unroll
+    for (int jt = 0; jt < 2; ++jt) {
+      sc[jt][0] = sc[jt][1] = sc[jt][2] = sc[jt][3] = 0.0f;
+      const int r = 16 * warp + 4 * (g >> 1) + 2 * jt + (g & 1);   // row of the K slab
+#pragma unroll
+      for (int j = 0; j < NCHUNK; ++j) {
+        const int chunk = 4 * j + t;
+        const uint32_t addr = kb + (uint32_t)(chunk >> 3) * (PAGE * 128) + (uint32_t)r * 128 +
+                              (uint32_t)(((chunk & 7) ^ (r & 7)) << 4);
+        const uint4 kv = lds128(addr);
+        uint32_t a[4];
+        a[0] = qa[j][0]; a[1] = qb[j][0]; a[2] = qa[j][1]; a[3] = qb[j][1];
+        mma_bf16(sc[jt], a, kv.x, kv.y);
+        a[0] = qa[j][2]; a[1] = qb[j][2]; a[2] = qa[j][3]; a[3] = qb[j][3];
+        mma_bf16(sc[jt], a, kv.z, kv.w);
+      }
+    }
+    // ---- mask and running maximum; column 2t+e of tile jt is key 4t + 2jt + e
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int jt = 0; jt < 2; ++jt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int idx = key0 + 4 * t + 2 * jt + e;
+        const bool ok = idx >= lo && idx < len;
+        sc[jt][e] = ok ? sc[jt][e] * scale_log2 : -INFINITY;
+        sc[jt][2 + e] = ok ? sc[jt][2 + e] * scale_log2 : -INFINITY;
+        mx0 = fmaxf(mx0, sc[jt][e]);
+        mx1 = fmaxf(mx1, sc[jt][2 + e]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    // the 16 keys of a warp may all lie outside the sequence or the window
+    const float ref0 = n0 == -INFINITY ? 0.0f : n0, ref1 = n1 == -INFINITY ? 0.0f : n1;
+    const float al0 = exp2f(m0 - ref0), al1 = HI ? exp2f(m1 - ref1) : 0.0f;
+    m0 = n0; m1 = n1;
+    uint32_t pa[4];
+    float r0 = 0.0f, r1 = 0.0f;
+#pragma unroll
+    for (int jt = 0; jt < 2; ++jt) {
+      const float p0 = exp2f(sc[jt][0] - ref0), p1 = exp2f(sc[jt][1] - ref0);
+      const float p2 = HI ? exp2f(sc[jt][2] - ref1) : 0.0f, p3 = HI ? exp2f(sc[jt][3] - ref1) : 0.0f;
+      r0 += p0 + p1;
+      r1 += p2 + p3;
+      pa[2 * jt] = pack_bf16(p0, p1);
+      pa[2 * jt + 1] = pack_bf16(p2, p3);
+    }
+    l0 = l0 * al0 + r0;
+    l1 = l1 * al1 + r1;
+    // ---- o = o * alpha + p . v; thread (g, t) reads v^T[dim 8i + g][keys 16*warp + 4t .. +3]
+#pragma unroll
+    for (int i2 = 0; i2 < NDT; ++i2) {
+      const int row = 8 * i2 + g;
+      const uint32_t addr = vb_ + (uint32_t)row * 128 +
+                            (uint32_t)(((2 * warp + (t >> 1)) ^ (row & 7)) << 4) + (uint32_t)(t & 1) * 8;
+      const uint2 vv = lds64(addr);
+      o[i2][0] *= al0; o[i2][1] *= al0; o[i2][2] *= al1; o[i2][3] *= al1;
+      mma_bf16(o[i2], pa, vv.x, vv.y);
+    }
+    __syncwarp();
+    if (lane == 0) td_mbar_arrive(&empty_bar[s]);
+  }
+
+  // ---- merge the four warps of the block (their keys are disjoint)
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();   // every warp is done with the stages; the first one now holds the merge
+  if (t == 0) {
+    sm_m[warp * 16 + g] = m0; sm_l[warp * 16 + g] = l0;
+    sm_m[warp * 16 + g + 8] = m1; sm_l[warp * 16 + g + 8] = l1;
+  }
+#pragma unroll
+  for (int i = 0; i < NDT; ++i) {
+    float* ro = sm_o + (size_t)(warp * 16 + g) * HEAD_DIM + 8 * i + 2 * t;
+    ro[0] = o[i][0]; ro[1] = o[i][1];
+    if (HI) { ro[8 * HEAD_DIM] = o[i][2]; ro[8 * HEAD_DIM + 1] = o[i][3]; }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HEAD_DIM; idx += TD_WARPS * 32) {
+    const int r = idx / HEAD_DIM, d = idx - r * HEAD_DIM;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < TD_WARPS; ++w) m = fmaxf(m, sm_m[w * 16 + r]);
+    float acc = 0.0f, l = 0.0f;
+#pragma unroll
+    for (int w = 0; w < TD_WARPS; ++w) {
+      const float wm = sm_m[w * 16 + r];
+      const float f = wm == -INFINITY ? 0.0f : exp2f(wm - m);
+      acc += f * sm_o[(size_t)(w * 16 + r) * HEAD_DIM + d];
+      l += f * sm_l[w * 16 + r];
+    }
+    float* dst = part + (((size_t)b * nh + kvh * G + r) * n_splits + split) * PART_STRIDE;
+    dst[d] = acc;
+    if (d == 0) { dst[HEAD_DIM] = m; dst[HEAD_DIM + 1] = l; }
+  }
+}
+
+// Merges the splits of one (sequence, head) and writes the normalised result.
+__global__ void __launch_bounds__(HEAD_DIM)
+FN(attn_decode_tma_combine_kernel)(const float* __restrict__ part, __nv_bfloat16* __restrict__ out,
+                                   int nh, int n_splits) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const float* src = part + ((size_t)b * nh + h) * n_splits * PART_STRIDE;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, src[s * PART_STRIDE + HEAD_DIM]);
+  float acc = 0.0f, l = 0.0f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float sm = src[s * PART_STRIDE + HEAD_DIM];
+    const float f = sm == -INFINITY ? 0.0f : exp2f(sm - m);
+    acc += f * src[s * PART_STRIDE + d];
+    l += f * src[s * PART_STRIDE + HEAD_DIM + 1];
+  }
+  out[((size_t)b * nh + h) * HEAD_DIM + d] = __float2bfloat16_rn(acc / l);
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor maps over the page storage (cached by address), launch.
+// ---------------------------------------------------------------------------
+typedef CUresult (*TdEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+
+static TdEncodeFn td_encode_fn() {
+  static TdEncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (TdEncodeFn)p;
+  });
+  return fn;
+}
+
+// rows x cols bfloat16, contiguous rows; boxes of 64 columns (128 bytes) x box_rows, 128-byte swizzle
+static bool td_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
+  typedef std::tuple<const void*, long long, long long, int> Key;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key(ptr, rows, cols, box_rows);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *map = it->second; return true; }
+  TdEncodeFn fn = td_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = m;
+  *map = m;
+  return true;
+}
+
+// As tl_attn_decode_hd<N>, plus the number of pages of the storage (for the tensor maps).
+// Returns -2 for sizes this kernel does not take.
+extern "C" int FN(tl_attn_decode_tma)(const void* q, const void* k_pages, const void* v_pages,
+                                      long long n_pages, void* out, float* part, const int* seq_len,
+                                      const int* seq_slot, const int* page_table, int table_stride,
+                                      int B, int nh, int nkv, int window, float scale, int n_splits,
+                                      cudaStream_t stream) {
+#if HEAD_DIM % 64 != 0
+  return -2;
+#else
+  if (B <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || n_splits > 65535 ||
+      nkv > 65535 || B > 65535 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+    return -2;
+  CUtensorMap tk, tv;
+  if (!td_make_map(&tk, k_pages, n_pages * nkv * PAGE, HEAD_DIM, PAGE)) return -2;
+  if (!td_make_map(&tv, v_pages, n_pages * nkv * HEAD_DIM, PAGE, HEAD_DIM)) return -2;
+  const size_t smem = 1024 + (size_t)TD_STAGES * TD_STAGE_BYTES + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(FN(attn_decode_tma_kernel)<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(FN(attn_decode_tma_kernel)<false>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(n_splits, nkv, B);
+  int st;
+  if (nh / nkv > 8)
+    st = tl_launch(FN(attn_decode_tma_kernel)<true>, grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
+                   (const __nv_bfloat16*)q, part, seq_len, seq_slot, page_table, table_stride, nh, nkv,
+                   window, scale_log2, n_splits);
+  else
+    st = tl_launch(FN(attn_decode_tma_kernel)<false>, grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
+                   (const __nv_bfloat16*)q, part, seq_len, seq_slot, page_table, table_stride, nh, nkv,
+                   window, scale_log2, n_splits);
+  if (st) return st;
+  return tl_launch(FN(attn_decode_tma_combine_kernel), dim3(nh, B), dim3(HEAD_DIM), 0, stream,
+                   (const float*)part, (__nv_bfloat16*)out, nh, n_splits);
+#endif
+}
+
+extern "C" int FN(tl_attn_tma_take_error)() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, tl_attn_tma_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(tl_attn_tma_error, &zero, sizeof(int));
+  return v;
+}
