@@ -320,9 +320,10 @@ def test_gemm_tensor_core(M, N, K):
     assert g.take_error() == 0
 
 
+@pytest.mark.parametrize("use_tma", [True, False])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, None), (8, 2, 128, 100), (4, 4, 64, 33),
                                                (3, 1, 32, None), (6, 3, 64, 64)])
-def test_attention_prefill_bf16(nh, nkv, hd, window):
+def test_attention_prefill_bf16(nh, nkv, hd, window, use_tma):
     """Tensor-core prefill kernel: sequences from scratch and continuing ones, lengths
     around the 16-query warps, the 64-query tiles and the 32-key groups."""
     from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
@@ -341,7 +342,8 @@ def test_attention_prefill_bf16(nh, nkv, hd, window):
     out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
     scale = 1 / math.sqrt(hd)
     att.prefill(q, pc.k_pages, pc.v_pages, out, seq_start, seq_len, pc.seq_slot, pc.table, B,
-                max(new), nh, nkv, window, scale)
+                max(new), nh, nkv, window, scale, use_tma=use_tma)
+    assert att.take_error() == 0
     got = out.cpu().double().view(T, nh, hd)
     qc = q.cpu().view(T, nh, hd)
     for b in range(B):
@@ -351,14 +353,14 @@ def test_attention_prefill_bf16(nh, nkv, hd, window):
             assert torch.allclose(got[tkn], ref, **_attn_tol(dtype)), f"seq {b} pos {pos}"
 
 
-@pytest.mark.parametrize("kernel", ["prefill_bf16", "generic_bf16", "generic_f32"])
+@pytest.mark.parametrize("kernel", ["prefill_bf16", "prefill_bf16_no_tma", "generic_bf16", "generic_f32"])
 def test_attention_far_key_stands_out_in_every_kernel(kernel):
     """The same idea as for the decode kernel, for the kernels that take many queries: one
     key far back matches the last queries strongly; with a window it sits on the window's
     first and last visible place and one place outside it."""
     from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
     dtype = torch.float32 if kernel.endswith("f32") else torch.bfloat16
-    nh, nkv, hd, n = 4, 2, 128 if kernel == "prefill_bf16" else 48, 300
+    nh, nkv, hd, n = 4, 2, 128 if kernel.startswith("prefill_bf16") else 48, 300
     scale = 1 / math.sqrt(hd)
     for window in (None, 100):
         last = n - 1
@@ -379,11 +381,11 @@ def test_attention_far_key_stands_out_in_every_kernel(kernel):
             out = torch.empty((n, nh * hd), dtype=dtype, device=DEV)
             pos = torch.arange(n, dtype=torch.int32, device=DEV)
             seq = torch.zeros(n, dtype=torch.int32, device=DEV)
-            if kernel == "prefill_bf16":
+            if kernel.startswith("prefill_bf16"):
                 AttentionBf16.get(hd).prefill(
                     q, pc.k_pages, pc.v_pages, out, torch.tensor([0, n], dtype=torch.int32, device=DEV),
                     torch.tensor([n], dtype=torch.int32, device=DEV), pc.seq_slot, pc.table, 1, n, nh, nkv,
-                    window, scale)
+                    window, scale, use_tma=not kernel.endswith("no_tma"))
             else:
                 _ops(dtype).attn_generic(q, pc.k_pages, pc.v_pages, out, pos, seq, pc.seq_slot, pc.table,
                                          nh, nkv, hd, window, scale)

@@ -60,6 +60,8 @@ class AttentionBf16:
             if head_dim % 64 == 0:
                 self._decode_tma = getattr(self.lib, f"tl_attn_decode_tma_hd{head_dim}")
                 self._decode_tma.restype = c_int
+                self._prefill_tma = getattr(self.lib, f"tl_attn_prefill_tma_hd{head_dim}")
+                self._prefill_tma.restype = c_int
                 self._tma_error = getattr(self.lib, f"tl_attn_tma_take_error_hd{head_dim}")
                 self._tma_error.restype = c_int
 
@@ -92,13 +94,22 @@ class AttentionBf16:
                "attn_decode")
 
     def prefill(self, q, k_pages, v_pages, out, seq_start, seq_len, seq_slot, page_table, n_seqs,
-                max_new, nh, nkv, window, scale) -> None:
+                max_new, nh, nkv, window, scale, use_tma: bool = True) -> None:
         """The new tokens of each sequence (packed, `seq_start` offsets) against the cache,
         which already holds their keys and values."""
         if self.lib is None:
             raise KernelError(f"no tensor-core prefill attention for head size {self.head_dim}")
         for t, n in ((q, "q"), (k_pages, "k pages"), (v_pages, "v pages"), (out, "out")):
             _need(t, torch.bfloat16, f"attn prefill {n}")
+        if getattr(self, "_decode_tma", None) is not None and use_tma:
+            st = self._prefill_tma(_ptr(q), _ptr(k_pages), _ptr(v_pages), c_longlong(k_pages.shape[0]),
+                                   _ptr(out), _ptr(seq_start), _ptr(seq_len), _ptr(seq_slot),
+                                   _ptr(page_table), c_int(page_table.stride(0)), c_int(n_seqs),
+                                   c_int(max_new), c_int(nh), c_int(nkv), c_int(window or 0),
+                                   c_float(scale), _stream())
+            if st != -2:
+                _check(st, "attn_prefill_tma")
+                return
         _check(self._prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(seq_start),
                              _ptr(seq_len), _ptr(seq_slot), _ptr(page_table),
                              c_int(page_table.stride(0)), c_int(n_seqs), c_int(max_new), c_int(nh),

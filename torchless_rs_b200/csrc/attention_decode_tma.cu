@@ -269,6 +269,178 @@ FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __gri
   }
 }
 
+// ---------------------------------------------------------------------------
+// Prefill with the same page pipeline: a block owns 64 consecutive queries of one head
+// (16 per warp) and walks over the pages that any of them can see; every warp reads the
+// fragments of the page it needs from shared memory.  Arithmetic as in
+// attention_prefill_bf16.cu.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(TD_WARPS * 32, 2)
+FN(attn_prefill_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                            const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                            const int* __restrict__ seq_start, const int* __restrict__ seq_len,
+                            const int* __restrict__ seq_slot, const int* __restrict__ page_table,
+                            int table_stride, int nh, int nkv, int window, float scale_log2) {
+  extern __shared__ uint8_t td_smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)td_smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + TD_STAGES * TD_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + TD_STAGES;
+  volatile int* abort_flag = (volatile int*)(empty_bar + TD_STAGES);
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TD_STAGES; ++s) { td_mbar_init(&full_bar[s], 1); td_mbar_init(&empty_bar[s], TD_WARPS); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tok0 = seq_start[b];
+  const int n_new = seq_start[b + 1] - tok0;
+  const int blk0 = blockIdx.x * (TD_WARPS * 16);       // first query of the block
+  if (blk0 >= n_new) return;
+  const int len = seq_len[b];
+  const int past = len - n_new;
+  const int kvh = h / (nh / nkv);
+  const int* table = page_table + (size_t)seq_slot[b] * table_stride;
+  // pages the block walks over: from the window start of its first query to its last query
+  const int blk_first = past + blk0, blk_last = past + min(blk0 + TD_WARPS * 16, n_new) - 1;
+  const int blk_lo = (window > 0 && blk_first - window + 1 > 0) ? blk_first - window + 1 : 0;
+  const int ps = blk_lo / PAGE;
+  const int n_pg = blk_last / PAGE - ps + 1;
+
+  auto issue = [&](int i) -> bool {
+    const int s = i % TD_STAGES;
+    if (!td_mbar_wait(&empty_bar[s], ((uint32_t)(i / TD_STAGES) & 1u) ^ 1u, abort_flag, 1)) return false;
+    const int slab = table[ps + i] * nkv + kvh;
+    uint8_t* st = smem + (size_t)s * TD_STAGE_BYTES;
+    td_mbar_expect_tx(&full_bar[s], TD_STAGE_BYTES);
+#pragma unroll
+    for (int sub = 0; sub < K_SUB; ++sub)
+      td_tma_load_2d(st + sub * (PAGE * 128), &tm_k, &full_bar[s], sub * 64, slab * PAGE);
+    td_tma_load_2d(st + K_BYTES, &tm_v, &full_bar[s], 0, slab * HEAD_DIM);
+    return true;
+  };
+  if (threadIdx.x == 0)
+    for (int i = 0; i < TD_STAGES - 1 && i < n_pg; ++i) issue(i);
+
+  // this warp's 16 queries; a warp past the end of the sequence only keeps the pipeline going
+  const int r0 = blk0 + warp * 16;
+  const bool active = r0 < n_new;
+  const int ra = min(r0 + g, n_new - 1), rb = min(r0 + g + 8, n_new - 1);
+  const int pa_pos = past + ra, pb_pos = past + rb;
+  uint32_t qa[NCHUNK][4], qb[NCHUNK][4];
+  {
+    const __nv_bfloat16* qra = q + ((size_t)(tok0 + ra) * nh + h) * HEAD_DIM;
+    const __nv_bfloat16* qrb = q + ((size_t)(tok0 + rb) * nh + h) * HEAD_DIM;
+#pragma unroll
+    for (int j = 0; j < NCHUNK; ++j) {
+      const uint4 va = ldg16(qra + (4 * j + t) * 8), vb = ldg16(qrb + (4 * j + t) * 8);
+      qa[j][0] = va.x; qa[j][1] = va.y; qa[j][2] = va.z; qa[j][3] = va.w;
+      qb[j][0] = vb.x; qb[j][1] = vb.y; qb[j][2] = vb.z; qb[j][3] = vb.w;
+    }
+  }
+  const int lo_a = (window > 0 && pa_pos - window + 1 > 0) ? pa_pos - window + 1 : 0;
+  const int lo_b = (window > 0 && pb_pos - window + 1 > 0) ? pb_pos - window + 1 : 0;
+  const int first_pos = past + min(r0, n_new - 1), last_pos = past + min(r0 + 15, n_new - 1);
+  const int lo_w = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+
+  float o[NDT][4];
+#pragma unroll
+  for (int i = 0; i < NDT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+
+  for (int i = 0; i < n_pg; ++i) {
+    if (threadIdx.x == 0 && i + TD_STAGES - 1 < n_pg) issue(i + TD_STAGES - 1);
+    __syncwarp();
+    const int s = i % TD_STAGES;
+    if (!td_mbar_wait(&full_bar[s], (uint32_t)(i / TD_STAGES) & 1u, abort_flag, 2)) break;
+    const uint32_t kb = td_smem_u32(smem + (size_t)s * TD_STAGE_BYTES);
+    const uint32_t vb_ = kb + K_BYTES;
+#pragma unroll
+    for (int grp = 0; grp < 2; ++grp) {
+      const int base = (ps + i) * PAGE + GROUP * grp;    // first key of this group of 32
+      if (!active || base > last_pos || base + GROUP <= lo_w) continue;   // nothing of it is visible
+      float sc[4][4];
+#pragma unroll
+      for (int jt = 0; jt < 4; ++jt) {
+        sc[jt][0] = sc[jt][1] = sc[jt][2] = sc[jt][3] = 0.0f;
+        const int r = GROUP * grp + 8 * (g >> 1) + 2 * jt + (g & 1);
+#pragma unroll
+        for (int j = 0; j < NCHUNK; ++j) {
+          const int chunk = 4 * j + t;
+          const uint4 kv = lds128(kb + (uint32_t)(chunk >> 3) * (PAGE * 128) + (uint32_t)r * 128 +
+                                  (uint32_t)(((chunk & 7) ^ (r & 7)) << 4));
+          uint32_t a[4];
+          a[0] = qa[j][0]; a[1] = qb[j][0]; a[2] = qa[j][1]; a[3] = qb[j][1];
+          mma_bf16(sc[jt], a, kv.x, kv.y);
+          a[0] = qa[j][2]; a[1] = qb[j][2]; a[2] = qa[j][3]; a[3] = qb[j][3];
+          mma_bf16(sc[jt], a, kv.z, kv.w);
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int jt = 0; jt < 4; ++jt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int idx = base + 8 * t + 2 * jt + e;
+          sc[jt][e] = (idx >= lo_a && idx <= pa_pos) ? sc[jt][e] * scale_log2 : -INFINITY;
+          sc[jt][2 + e] = (idx >= lo_b && idx <= pb_pos) ? sc[jt][2 + e] * scale_log2 : -INFINITY;
+          mx0 = fmaxf(mx0, sc[jt][e]);
+          mx1 = fmaxf(mx1, sc[jt][2 + e]);
+        }
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      const float ref0 = n0 == -INFINITY ? 0.0f : n0, ref1 = n1 == -INFINITY ? 0.0f : n1;
+      const float al0 = exp2f(m0 - ref0), al1 = exp2f(m1 - ref1);
+      m0 = n0; m1 = n1;
+      uint32_t pa[2][4];
+      float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+      for (int jt = 0; jt < 4; ++jt) {
+        const float p0 = exp2f(sc[jt][0] - ref0), p1 = exp2f(sc[jt][1] - ref0);
+        const float p2 = exp2f(sc[jt][2] - ref1), p3 = exp2f(sc[jt][3] - ref1);
+        sum0 += p0 + p1;
+        sum1 += p2 + p3;
+        pa[jt >> 1][(jt & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pa[jt >> 1][(jt & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+      l0 = l0 * al0 + sum0;
+      l1 = l1 * al1 + sum1;
+#pragma unroll
+      for (int i2 = 0; i2 < NDT; ++i2) {
+        const int row = 8 * i2 + g;
+        const uint4 vv = lds128(vb_ + (uint32_t)row * 128 + (uint32_t)(((4 * grp + t) ^ (row & 7)) << 4));
+        o[i2][0] *= al0; o[i2][1] *= al0; o[i2][2] *= al1; o[i2][3] *= al1;
+        mma_bf16(o[i2], pa[0], vv.x, vv.y);
+        mma_bf16(o[i2], pa[1], vv.z, vv.w);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) td_mbar_arrive(&empty_bar[s]);
+  }
+  if (!active) return;
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
+  const bool wa = r0 + g < n_new, wb = r0 + g + 8 < n_new;
+  __nv_bfloat16* oa = out + ((size_t)(tok0 + ra) * nh + h) * HEAD_DIM;
+  __nv_bfloat16* ob = out + ((size_t)(tok0 + rb) * nh + h) * HEAD_DIM;
+#pragma unroll
+  for (int i = 0; i < NDT; ++i) {
+    if (wa) *reinterpret_cast<uint32_t*>(oa + 8 * i + 2 * t) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    if (wb) *reinterpret_cast<uint32_t*>(ob + 8 * i + 2 * t) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+  }
+}
+
 // Merges the splits of one (sequence, head) and writes the normalised result.
 __global__ void __launch_bounds__(HEAD_DIM)
 FN(attn_decode_tma_combine_kernel)(const float* __restrict__ part, __nv_bfloat16* __restrict__ out,
@@ -378,6 +550,37 @@ extern "C" int FN(tl_attn_decode_tma)(const void* q, const void* k_pages, const 
   if (st) return st;
   return tl_launch(FN(attn_decode_tma_combine_kernel), dim3(nh, B), dim3(HEAD_DIM), 0, stream,
                    (const float*)part, (__nv_bfloat16*)out, nh, n_splits);
+#endif
+}
+
+// As tl_attn_prefill_hd<N>, plus the number of pages of the storage.
+extern "C" int FN(tl_attn_prefill_tma)(const void* q, const void* k_pages, const void* v_pages,
+                                       long long n_pages, void* out, const int* seq_start,
+                                       const int* seq_len, const int* seq_slot, const int* page_table,
+                                       int table_stride, int B, int max_new, int nh, int nkv,
+                                       int window, float scale, cudaStream_t stream) {
+#if HEAD_DIM % 64 != 0
+  return -2;
+#else
+  if (B <= 0 || max_new <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh > 65535 || B > 65535 || ((uintptr_t)k_pages & 15) ||
+      ((uintptr_t)v_pages & 15))
+    return -2;
+  CUtensorMap tk, tv;
+  if (!td_make_map(&tk, k_pages, n_pages * nkv * PAGE, HEAD_DIM, PAGE)) return -2;
+  if (!td_make_map(&tv, v_pages, n_pages * nkv * HEAD_DIM, PAGE, HEAD_DIM)) return -2;
+  const size_t smem = 1024 + (size_t)TD_STAGES * TD_STAGE_BYTES + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(FN(attn_prefill_tma_kernel),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_new + TD_WARPS * 16 - 1) / (TD_WARPS * 16), nh, B);
+  return tl_launch(FN(attn_prefill_tma_kernel), grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
+                   (const __nv_bfloat16*)q, (__nv_bfloat16*)out, seq_start, seq_len, seq_slot,
+                   page_table, table_stride, nh, nkv, window, scale * 1.4426950408889634f);
 #endif
 }
 
