@@ -151,8 +151,8 @@ def decode_device_timed(model, batch: int, steps: int, warmup: int, end_context:
 def decode_end_to_end(model, batch: int, steps: int, warmup: int, end_context: int):
     """The same through `Model.generate`: host token ids in, host token ids out at every
     step.  Real prompts are prefilled first (not timed); the time runs on the host from
-    the token emitted after `warmup` decode steps to the last one, with a device
-    synchronisation at each stamp."""
+    the token emitted after `warmup` decode steps to the last one; a stamp is taken when the
+    host holds the step's tokens."""
     import torch
     eng = model.engine
     n_prompt = end_context - steps - warmup - 1
@@ -160,8 +160,7 @@ def decode_end_to_end(model, batch: int, steps: int, warmup: int, end_context: i
     stamps = []
 
     def on_token(i, tok):
-        if i == batch - 1:
-            torch.cuda.synchronize()
+        if i == batch - 1:    # the host holds this step's tokens now (they were read from the device)
             stamps.append(time.perf_counter())
     model.generate(prompts, max_tokens=steps + warmup + 1, temperature=0.0, stop_ids=(),
                    on_token=on_token)

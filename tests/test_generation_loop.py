@@ -35,7 +35,10 @@ class ScriptedEngine:
         self.free = sorted(self.free + list(slots))
         self.log.append(("end", tuple(slots)))
 
-    def step(self, slots, tokens, want="last"):
+    def step(self, slots, tokens, want="last", from_device=None):
+        if from_device is not None:
+            src, idx = from_device
+            tokens = [[src[j]] for j in idx]
         assert want == "last" and len(slots) == len(tokens)
         for s, t in zip(slots, tokens):
             assert s in self.held
@@ -148,3 +151,61 @@ def test_uniform_numbers_do_not_depend_on_batching():
         want = sorted(uniform_for(5, i, k) for i in range(3) for k in range(3))
         assert flat == want
     assert 0.0 <= uniform_for(1, 2, 3) < 1.0 and uniform_for(1, 2, 3) != uniform_for(1, 2, 4)
+
+
+class AheadReader:
+    """Says that reading may overlap the next step; here both ends are immediate."""
+    overlapped = True
+
+    def start(self, selected):
+        return list(selected)
+
+    def finish(self, handle):
+        return handle
+
+
+def test_one_step_ahead_gives_the_same_tokens_and_at_most_one_extra_step():
+    prompts = [[1, 2, 3, 4, 5], [9], [7, 7, 7], [4, 4], [30, 2, 2, 2, 2, 2, 2]]
+    stop = {13, 21}
+    for mb in (2, 5):
+        eng = ScriptedEngine(n_slots=mb)
+        eng.takes_device_tokens = True
+        res = generate(eng, select, prompts, 12, SamplingParams.greedy(), stop, cache_tokens=10 ** 6,
+                       max_batch=mb, reader=AheadReader())
+        for i, p in enumerate(prompts):
+            toks, stopped = expected(p, 12, stop)
+            assert res[i].tokens == toks and res[i].stopped_at_eos == stopped, (mb, i)
+        assert not eng.held
+        # a sequence runs one step per token it feeds back; one more only if a stop token
+        # ended it (learnt one step late); never beyond max_tokens
+        fed = {}
+        slot_req = {}
+        for e in eng.log:
+            if e[0] == "start":
+                starts = e[1]
+            if e[0] == "step":
+                for s_ in e[1]:
+                    fed[s_] = fed.get(s_, 0) + 1
+        total_steps = sum(len(e[1]) for e in eng.log if e[0] == "step")
+        needed = sum(1 + max(len(r.tokens) - (0 if r.stopped_at_eos else 1), 0) for r in res)
+        extra = total_steps - needed
+        assert 0 <= extra <= sum(1 for r in res if r.stopped_at_eos), (mb, extra)
+
+
+def test_ahead_with_sampling_uses_the_same_uniform_numbers():
+    got = {}
+
+    def sel(logits, params, uniforms):
+        for (slot, length, last), u in zip(logits, uniforms):
+            got.setdefault((slot, length), u)
+        return select(logits, params, uniforms)
+    prompts = [[1], [2, 5], [3]]
+    runs = []
+    for reader in (None, AheadReader()):
+        got.clear()
+        eng = ScriptedEngine(3)
+        eng.takes_device_tokens = True
+        generate(eng, sel, prompts, 4, SamplingParams(temperature=0.8), (), seed=5, cache_tokens=10 ** 6,
+                 max_batch=3, reader=reader, to_host=list)
+        runs.append(dict(got))
+    assert runs[0] == runs[1]

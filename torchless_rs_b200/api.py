@@ -35,6 +35,32 @@ def parse_dtype(dtype: Union[str, torch.dtype]) -> torch.dtype:
     raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
 
 
+class OverlappedReader:
+    """Copies selected tokens to pinned host memory without waiting; `finish` waits for
+    that copy only.  Two buffers in rotation, since one step is launched ahead."""
+    overlapped = True
+
+    def __init__(self, rows: int = 256):
+        self.bufs = [torch.empty(rows, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        self.events = [torch.cuda.Event() for _ in range(3)]
+        self.turn = 0
+
+    def start(self, selected: torch.Tensor):
+        n = selected.numel()
+        self.turn = (self.turn + 1) % 3
+        if self.bufs[self.turn].numel() < n:
+            self.bufs = [torch.empty(2 * n, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        buf, ev = self.bufs[self.turn], self.events[self.turn]
+        buf[:n].copy_(selected, non_blocking=True)
+        ev.record()
+        return buf, n, ev
+
+    def finish(self, handle) -> List[int]:
+        buf, n, ev = handle
+        ev.synchronize()
+        return buf[:n].tolist()
+
+
 class Model:
     """A loaded model with its cache.  `config` is the typed configuration;
     `engine` gives `step`, `start_sequences`, `end_sequences`."""
@@ -43,6 +69,7 @@ class Model:
         self.config = config
         self.engine = engine
         self._sampler = None
+        self._reader = None
 
     @property
     def sampler(self):
@@ -62,8 +89,10 @@ class Model:
         params = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p)
         if stop_ids is None:
             stop_ids = self.engine.spec.stop_token_ids
+        if self._reader is None:
+            self._reader = OverlappedReader()
         return _generate(self.engine, self.sampler.select, prompts, max_tokens, params, stop_ids,
-                         seed, on_token, max_batch=max_batch)
+                         seed, on_token, max_batch=max_batch, reader=self._reader)
 
     def step(self, slots, tokens, want="last"):
         return self.engine.step(slots, tokens, want)

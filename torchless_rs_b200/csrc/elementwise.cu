@@ -7,22 +7,28 @@
 // Embedding: x[t, :] = table[tokens[t], :], no scaling
 // (reference: src/model/modules/embedding.rs:15-21).
 // ---------------------------------------------------------------------------
-__global__ void embed_kernel(const int* __restrict__ tokens, const act_t* __restrict__ table,
+// A token may also be taken from a device buffer (the tokens that the previous step selected):
+// with `token_src` given, token t is token_src[token_from[t]] wherever token_from[t] >= 0.
+__global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ token_from,
+                             const int* __restrict__ token_src, const act_t* __restrict__ table,
                              float* __restrict__ x, int H, int vocab) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   int tok = tokens[t];
+  if (token_src != nullptr && token_from[t] >= 0) tok = token_src[token_from[t]];
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // the host has checked the range already
   const act_t* src = table + (size_t)tok * H;
   float* dst = x + (size_t)t * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32(src[i]);
 }
 
-extern "C" int TL_NAME(tl_embed)(const int* tokens, const void* table, float* x, int T, int H,
-                                 int vocab, cudaStream_t stream) {
+extern "C" int TL_NAME(tl_embed)(const int* tokens, const int* token_from, const int* token_src,
+                                 const void* table, float* x, int T, int H, int vocab,
+                                 cudaStream_t stream) {
   if (T <= 0) return 0;
-  return tl_launch(embed_kernel, dim3(T), dim3(256), 0, stream, tokens, (const act_t*)table, x, H, vocab);
+  return tl_launch(embed_kernel, dim3(T), dim3(256), 0, stream, tokens, token_from, token_src,
+                   (const act_t*)table, x, H, vocab);
 }
 
 // ---------------------------------------------------------------------------

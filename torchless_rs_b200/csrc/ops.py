@@ -87,12 +87,20 @@ class CoreOps:
             setattr(self, "_" + base, fn)
 
     # x[t, :] = table[tokens[t], :]
-    def embed(self, tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor) -> None:
+    def embed(self, tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor,
+              token_from: Optional[torch.Tensor] = None,
+              token_src: Optional[torch.Tensor] = None) -> None:
+        """With `token_src` (int32 on the device), token t is token_src[token_from[t]] wherever
+        token_from[t] >= 0, else tokens[t]."""
         _need(tokens, torch.int32, "embed tokens")
         _need(table, self.act_dtype, "embed table")
         _need(x, torch.float32, "embed out")
+        if token_src is not None:
+            _need(token_src, torch.int32, "embed token source")
+            _need(token_from, torch.int32, "embed token index")
         T, H = x.shape
-        _check(self._tl_embed(_ptr(tokens), _ptr(table), _ptr(x), c_int(T), c_int(H),
+        _check(self._tl_embed(_ptr(tokens), _ptr(token_from if token_src is not None else None),
+                              _ptr(token_src), _ptr(table), _ptr(x), c_int(T), c_int(H),
                               c_int(table.shape[0]), _stream()), "embed")
 
     def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

@@ -31,9 +31,11 @@ class StepBatch:
     seq_start: torch.Tensor
     seq_len: torch.Tensor
     want_rows: torch.Tensor
+    token_from: torch.Tensor     # [T] index into `token_src`, or -1 for "use tokens[t]"
     slots: List[int]
     past_lens: List[int]
     new_lens: List[int]
+    token_src: Optional[torch.Tensor] = None   # device int32: tokens selected by the previous step
 
 
 def layout_step(past_lens: Sequence[int], counts: Sequence[int], slots: Sequence[int],
@@ -58,7 +60,8 @@ def layout_step(past_lens: Sequence[int], counts: Sequence[int], slots: Sequence
         tokens=toks.astype(np.int32), token_seq=token_seq, token_pos=token_pos,
         seq_slot=np.asarray(slots, dtype=np.int32), seq_start=seq_start,
         seq_len=np.asarray([p + c for p, c in zip(past_lens, counts)], dtype=np.int32),
-        want_rows=np.asarray(want_rows, dtype=np.int32))
+        want_rows=np.asarray(want_rows, dtype=np.int32),
+        token_from=np.full(T, -1, dtype=np.int32))
 
 
 class BatchStager:
@@ -66,7 +69,8 @@ class BatchStager:
     device with one copy.  The device buffer keeps its address, so views taken for
     the same sizes stay valid from step to step."""
 
-    FIELDS = ("tokens", "token_seq", "token_pos", "seq_slot", "seq_start", "seq_len", "want_rows")
+    FIELDS = ("tokens", "token_seq", "token_pos", "seq_slot", "seq_start", "seq_len", "want_rows",
+              "token_from")
 
     RING = 4   # pinned buffers in rotation, so the host can prepare a step while earlier copies run
 

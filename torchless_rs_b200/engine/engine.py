@@ -38,6 +38,7 @@ class Engine:
         self.model.bind_cache(self.cache)
         self.stager = BatchStager(rt.device)
         self.vocab_size = spec.vocab_size
+        self.takes_device_tokens = True   # step(..., from_device=...) is supported
         self.use_graphs = use_graphs
         self._graphs = {}      # key -> (CUDA graph, logits view)
         self._seen = set()     # keys that have run once without a graph
@@ -55,16 +56,27 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step ----------------------------------------------------------------------
-    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: Union[str, Sequence[Sequence[int]]] = "last") -> Optional[torch.Tensor]:
+    def step(self, slots: Sequence[int], tokens: Optional[Sequence[Sequence[int]]] = None,
+             want: Union[str, Sequence[Sequence[int]]] = "last",
+             from_device=None) -> Optional[torch.Tensor]:
         """Runs `tokens[b]` as the next tokens of the sequence in `slots[b]` and
         returns the 32-bit logits [wanted, vocab] on the device, in the order of the
         sequences and of their wanted places (`want[b]`: indices into `tokens[b]`;
         "last": the last token of each; "all"; "none").  The returned tensor is a
-        view of a buffer that the next step overwrites."""
+        view of a buffer that the next step overwrites.
+
+        `from_device` = (source, indices) instead of `tokens`: every sequence goes on by the
+        one token source[indices[b]], where `source` is an int32 tensor on the device (the
+        tokens a sampler selected).  The host then need not know the tokens to launch the step."""
         B = len(slots)
         if B == 0:
             return None
+        token_src = None
+        if from_device is not None:
+            token_src, src_index = from_device
+            if len(src_index) != B:
+                raise ValueError("one source index per slot is needed")
+            tokens = [[0]] * B
         if len(tokens) != B:
             raise ValueError("one token list per slot is needed")
         counts = [len(t) for t in tokens]
@@ -78,12 +90,15 @@ class Engine:
             want = [[] for _ in counts]
         past = [self.cache.length(s) for s in slots]
         arrays = layout_step(past, counts, slots, tokens, want)
+        if token_src is not None:
+            arrays["token_from"] = np.asarray(src_index, dtype=np.int32)
         toks = arrays["tokens"]
         if toks.size and (toks.min() < 0 or toks.max() >= self.vocab_size):
             raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
         new_lens = [p + c for p, c in zip(past, counts)]
         self.cache.prepare(slots, new_lens)
         batch = self.stager.stage(arrays, slots, past, is_decode=all(c == 1 for c in counts))
+        batch.token_src = token_src
         logits = self._forward(batch)
         self.cache.commit(slots, new_lens)
         return logits
@@ -95,7 +110,7 @@ class Engine:
         if not (self.use_graphs and batch.is_decode and self.model.graph_safe):
             return self.model.forward(batch)
         key = (batch.n_seqs, batch.n_want, batch.len_bucket, self.rt.workspace.generation,
-               batch.tokens.data_ptr())
+               batch.tokens.data_ptr(), batch.token_src.data_ptr() if batch.token_src is not None else 0)
         hit = self._graphs.get(key)
         if hit is not None:
             hit[0].replay()

@@ -63,17 +63,38 @@ def plan_batches(prompt_lens: Sequence[int], max_tokens: int, cache_tokens: int,
     return batches
 
 
+class SyncReader:
+    """Brings selected tokens to the host at once (`to_host` turns what `select` returned
+    into a list of ints)."""
+    overlapped = False
+
+    def __init__(self, to_host: Callable = lambda t: t.tolist()):
+        self.to_host = to_host
+
+    def start(self, selected):
+        return selected
+
+    def finish(self, handle) -> List[int]:
+        return [int(t) for t in self.to_host(handle)]
+
+
 def generate(engine, select: Callable, prompts: Sequence[Sequence[int]], max_tokens: int,
              params: SamplingParams = SamplingParams(), stop_ids: Sequence[int] = (),
              seed: int = 0, on_token: Optional[Callable[[int, int], None]] = None,
              cache_tokens: Optional[int] = None, max_batch: Optional[int] = None,
-             to_host: Callable = lambda t: t.tolist()) -> List[GenerationResult]:
+             to_host: Callable = lambda t: t.tolist(), reader=None) -> List[GenerationResult]:
     """Generates up to `max_tokens` tokens for every prompt (lists of token ids).
 
     A stop token ends its sequence and is not part of the result
     (src/sampler/mod.rs:289-294).  `on_token(request index, token)` is called for
     every emitted token.  The uniform number of a draw depends on (seed, request
-    index, number of tokens generated so far), not on how requests were batched."""
+    index, number of tokens generated so far), not on how requests were batched.
+
+    `reader` brings the selected tokens of a step to the host: `start(selected)` and
+    `finish(handle) -> list`.  If it says `overlapped` and the engine's `step` takes
+    `from_device`, the next step is launched with the tokens still on the device and the
+    host reads them while that step runs; a sequence that turns out to have ended then
+    has run one step too many, whose result is dropped."""
     if max_tokens < 0:
         raise ValueError("max_tokens must be >= 0")
     for i, p in enumerate(prompts):
@@ -83,42 +104,87 @@ def generate(engine, select: Callable, prompts: Sequence[Sequence[int]], max_tok
     results = [GenerationResult(prompt_len=len(p)) for p in prompts]
     if max_tokens == 0 or not prompts:
         return results
+    reader = reader if reader is not None else SyncReader(to_host)
+    ahead = bool(getattr(reader, "overlapped", False)) and bool(getattr(engine, "takes_device_tokens", False))
     cache_tokens = cache_tokens if cache_tokens is not None else engine.cache.max_tokens
     max_batch = max_batch if max_batch is not None else engine.cache.max_slots
+
+    def uniforms_for(reqs, extra: int):
+        if params.is_greedy:
+            return None
+        return [uniform_for(seed, i, len(results[i].tokens) + extra) for i in reqs]
+
+    def take(i: int, tok: int) -> bool:
+        """Books one selected token of request i; True if the sequence goes on."""
+        r = results[i]
+        if tok in stop:
+            r.stopped_at_eos = True
+            return False
+        r.tokens.append(tok)
+        if on_token is not None:
+            on_token(i, tok)
+        return len(r.tokens) < max_tokens
+
     for batch in plan_batches([len(p) for p in prompts], max_tokens, cache_tokens, max_batch):
         slots = engine.start_sequences(len(batch))
-        live = list(zip(batch, slots))          # (request index, slot), in request order
-        feed = [list(prompts[i]) for i in batch]
+        held = set(slots)
+
+        def end(ss):
+            ss = [s for s in ss if s in held]
+            if ss:
+                held.difference_update(ss)
+                engine.end_sequences(ss)   # ends earlier: its slot is free at once
         try:
+            live = list(zip(batch, slots))          # (request index, slot), in request order
+            logits = engine.step([s for _, s in live], [list(prompts[i]) for i in batch], want="last")
+            selected = select(logits, params, uniforms_for([i for i, _ in live], 0))
+            handle = reader.start(selected)
+            where = list(range(len(live)))          # place of each live sequence in `selected`
             while live:
-                logits = engine.step([s for _, s in live], feed, want="last")
-                uniforms = None
-                if not params.is_greedy:
-                    uniforms = [uniform_for(seed, i, len(results[i].tokens)) for i, _ in live]
-                chosen = to_host(select(logits, params, uniforms))
-                nxt_live, feed, ended = [], [], []
-                for (i, s), tok in zip(live, chosen):
-                    r = results[i]
-                    tok = int(tok)
-                    if tok in stop:
-                        r.stopped_at_eos = True
+                launched = None
+                if ahead:
+                    # every sequence that can still go on runs its next step now, fed from the
+                    # device; whether its last token was a stop token is learnt below
+                    cand = [(w, i, s) for w, (i, s) in zip(where, live)
+                            if len(results[i].tokens) + 1 < max_tokens]
+                    if cand:
+                        logits = engine.step([s for _, _, s in cand], None, want="last",
+                                             from_device=(selected, [w for w, _, _ in cand]))
+                        nxt = select(logits, params, uniforms_for([i for _, i, _ in cand], 1))
+                        launched = (cand, nxt, reader.start(nxt))
+                toks = reader.finish(handle)
+                going, ended = {}, []
+                for w, (i, s) in zip(where, live):
+                    if take(i, toks[w]):
+                        going[i] = s
+                    else:
                         ended.append(s)
-                        continue
-                    r.tokens.append(tok)
-                    if on_token is not None:
-                        on_token(i, tok)
-                    if len(r.tokens) >= max_tokens:
-                        ended.append(s)
-                        continue
-                    r.steps += 1
-                    nxt_live.append((i, s))
-                    feed.append([tok])
-                if ended:
-                    engine.end_sequences(ended)   # ends earlier: its slot is free at once
-                live = nxt_live
+                end(ended)
+                if ahead:
+                    if launched is None:
+                        end(list(going.values()))
+                        break
+                    cand, selected, handle = launched
+                    live, where = [], []
+                    for place, (_, i, s) in enumerate(cand):
+                        if i in going:
+                            results[i].steps += 1
+                            live.append((i, s))
+                            where.append(place)
+                else:
+                    live = list(going.items())
+                    if not live:
+                        break
+                    for i, _ in live:
+                        results[i].steps += 1
+                    logits = engine.step([s for _, s in live], [[results[i].tokens[-1]] for i, _ in live],
+                                         want="last")
+                    selected = select(logits, params, uniforms_for([i for i, _ in live], 0))
+                    handle = reader.start(selected)
+                    where = list(range(len(live)))
+            end(list(held))
         except BaseException:
-            held = [s for _, s in live]
             if held:
-                engine.end_sequences(held)
+                engine.end_sequences(list(held))
             raise
     return results

@@ -122,7 +122,7 @@ class DecoderModel:
         rt, ws = self.rt, self.rt.workspace
         T, H = batch.n_tokens, self.spec.hidden_size
         x = ws.get("stream", (T, H), torch.float32)
-        rt.ops.embed(batch.tokens, self.embedding, x)
+        rt.ops.embed(batch.tokens, self.embedding, x, batch.token_from, batch.token_src)
         order = self.spec.order
         carry = None
         for k, i in enumerate(order):

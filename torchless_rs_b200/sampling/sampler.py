@@ -18,7 +18,10 @@ class Sampler:
     def _resize(self, rows: int) -> None:
         self.max_rows = rows
         self.out = torch.empty(rows, dtype=torch.int32, device=self.device)
-        self.uniform_host = torch.empty(rows, dtype=torch.float32, pin_memory=True)
+        # pinned staging in rotation: a select may be enqueued before the previous copy has run
+        self.uniform_hosts = [torch.empty(rows, dtype=torch.float32, pin_memory=True) for _ in range(4)]
+        self.uniform_events = [None] * 4
+        self.turn = 0
         self.uniform_dev = torch.empty(rows, dtype=torch.float32, device=self.device)
 
     def select(self, logits: torch.Tensor, params: SamplingParams,
@@ -35,8 +38,15 @@ class Sampler:
             return out
         if uniforms is None or len(uniforms) != rows:
             raise ValueError("sampling with a temperature needs one uniform number per row")
-        self.uniform_host[:rows] = torch.as_tensor(list(uniforms), dtype=torch.float32)
-        self.uniform_dev[:rows].copy_(self.uniform_host[:rows], non_blocking=True)
+        self.turn = (self.turn + 1) % 4
+        if self.uniform_events[self.turn] is not None:
+            self.uniform_events[self.turn].synchronize()
+        host = self.uniform_hosts[self.turn]
+        host[:rows] = torch.as_tensor(list(uniforms), dtype=torch.float32)
+        self.uniform_dev[:rows].copy_(host[:rows], non_blocking=True)
+        ev = self.uniform_events[self.turn] or torch.cuda.Event()
+        ev.record()
+        self.uniform_events[self.turn] = ev
         self.ops.sample(logits, float(params.temperature), int(params.top_k or 0),
                         float(params.top_p if params.top_p is not None else 0.0),
                         self.uniform_dev, out)
