@@ -60,6 +60,11 @@ class PagedGroup:
         self.first_live = [0] * max_slots   # first table column that still holds a page
         self.n_cols = [0] * max_slots       # table columns filled so far
         self._dirty: set = set()
+        # rows on their way to the device are snapshots in pinned memory (several in rotation):
+        # the host may change the table again before an earlier copy has run
+        self._staging = None
+        self._staging_events = []
+        self._turn = 0
 
     def pages_needed(self, slot: int, new_len: int) -> int:
         return max(0, pages_for(new_len) - self.n_cols[slot])
@@ -106,13 +111,27 @@ class PagedGroup:
             return
         rows = sorted(self._dirty)
         self._dirty.clear()
-        idx = torch.as_tensor(rows, dtype=torch.long)
-        src = torch.from_numpy(self.table_host[rows])
-        if self.table_dev.is_cuda:
-            self.table_dev.index_copy_(0, idx.to(self.table_dev.device, non_blocking=True),
-                                       src.to(self.table_dev.device, non_blocking=True))
-        else:
-            self.table_dev.index_copy_(0, idx, src)
+        if not self.table_dev.is_cuda:
+            idx = torch.as_tensor(rows, dtype=torch.long)
+            self.table_dev.index_copy_(0, idx, torch.from_numpy(self.table_host[rows]))
+            return
+        chunk = 32   # rows per snapshot buffer
+        if self._staging is None:
+            self._staging = torch.empty((4, chunk, self.table_host.shape[1]), dtype=torch.int32,
+                                        pin_memory=True)
+            self._staging_events = [None] * 4
+        for c0 in range(0, len(rows), chunk):
+            self._turn = (self._turn + 1) % 4
+            if self._staging_events[self._turn] is not None:
+                self._staging_events[self._turn].synchronize()
+            stage = self._staging[self._turn]
+            stage_np = stage.numpy()
+            for j, r in enumerate(rows[c0:c0 + chunk]):
+                stage_np[j] = self.table_host[r]
+                self.table_dev[r].copy_(stage[j], non_blocking=True)
+            ev = self._staging_events[self._turn] or torch.cuda.Event()
+            ev.record()
+            self._staging_events[self._turn] = ev
 
     def view(self, layer: int) -> PagedView:
         i = self.layers.index(layer)
