@@ -270,7 +270,7 @@ def main() -> int:
             "l2": "inputs_exceed_l2", "peaks": peaks["source"],
         },
         "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": 4 * (4 * ((B + 3) // 4 * 4) + 2 * ((B + 4) // 4 * 4) + 4),
+                "h2d_bytes_per_step": 4 * (7 * ((B + 3) // 4 * 4) + (B + 4) // 4 * 4),
                 "d2h_bytes_per_step": 4 * B},
         "gpu_launches": launches,
         "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,

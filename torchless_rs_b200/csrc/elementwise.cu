@@ -110,18 +110,30 @@ __global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
                                         const int* __restrict__ page_table, int table_stride,
                                         const float* __restrict__ inv_freq, int style, int nh,
                                         int nkv, int hd, int heads_per_block) {
-  // grid (tokens, groups of heads); heads count query heads, then key heads, then value heads
+  // grid (tokens, groups of heads); heads count query heads, then key heads, then value heads.
+  // A warp takes every fourth head of its group, so that sine and cosine of a (position, i)
+  // are computed once per warp and used for all its heads.
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int pos = token_pos[t];
   const int half = hd >> 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const int total_heads = nh + (k_pages ? 2 * nkv : 0);
-  const int h_end = min((int)(blockIdx.y + 1) * heads_per_block, total_heads);
+  const int h_begin = blockIdx.y * heads_per_block;
+  const int h_end = min(h_begin + heads_per_block, total_heads);
   int page = -1;
   if (k_pages) page = page_table[(size_t)seq_slot[token_seq[t]] * table_stride + pos / TL_PAGE];
   const float fpos = (float)pos;
-  for (int h = blockIdx.y * heads_per_block; h < h_end; ++h) {
+  // up to 256 / 2 / 32 = 4 rotation pairs per lane
+  float cs[4], sn[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = lane + 32 * j;
+    cs[j] = 1.0f; sn[j] = 0.0f;
+    if (inv_freq && i < half) sincosf(fpos * inv_freq[i], &sn[j], &cs[j]);
+  }
+  for (int h = h_begin + warp; h < h_end; h += n_warps) {
     const float* row = qkv + (size_t)t * ld + (size_t)h * hd;
     if (h >= nh && page < 0) continue;
     const int kvh = h < nh ? 0 : (h - nh < nkv ? h - nh : h - nh - nkv);
@@ -129,24 +141,20 @@ __global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
     if (h < nh + nkv) {
       act_t* dst = h < nh ? q_out + (size_t)t * nh * hd + (size_t)h * hd
                           : k_pages + page_base + (size_t)(pos % TL_PAGE) * hd;
-      for (int i = threadIdx.x; i < half; i += blockDim.x) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= half) break;
         const int d0 = style == 0 ? i : 2 * i;
         const int d1 = style == 0 ? i + half : 2 * i + 1;
         const float a = row[d0], b = row[d1];
-        float ra = a, rb = b;
-        if (inv_freq) {
-          float s, c;
-          sincosf(fpos * inv_freq[i], &s, &c);
-          ra = a * c - b * s;
-          rb = a * s + b * c;
-        }
-        dst[d0] = from_f32<act_t>(ra);
-        dst[d1] = from_f32<act_t>(rb);
+        dst[d0] = from_f32<act_t>(a * cs[j] - b * sn[j]);
+        dst[d1] = from_f32<act_t>(a * sn[j] + b * cs[j]);
       }
     } else {
       // values lie transposed in a page: [hd][TL_PAGE]
       act_t* dst = v_pages + page_base + (pos % TL_PAGE);
-      for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[(size_t)d * TL_PAGE] = from_f32<act_t>(row[d]);
+      for (int d = lane; d < hd; d += 32) dst[(size_t)d * TL_PAGE] = from_f32<act_t>(row[d]);
     }
   }
 }
@@ -158,14 +166,14 @@ extern "C" int TL_NAME(tl_rope_cache_write)(const float* qkv, int ld, void* q_ou
                                             const float* inv_freq, int style, int T, int nh,
                                             int nkv, int hd, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd & 1) return TL_ERR_BAD_ARG;
+  if ((hd & 1) || hd > 256) return TL_ERR_BAD_ARG;
   const int heads = nh + (k_pages ? 2 * nkv : 0);
-  // few tokens: one head per block, for parallelism; many tokens: fewer, larger blocks
-  const int per_block = T >= 256 ? 8 : 1;
+  // few tokens: one warp per (token, head), for parallelism; many tokens: one block per token
+  const int per_block = T >= 256 ? heads : 1;
   const int groups = (heads + per_block - 1) / per_block;
   if (groups > 65535) return TL_ERR_UNSUPPORTED;
   dim3 grid(T, groups);
-  return tl_launch(rope_cache_write_kernel, grid, dim3(64), 0, stream, qkv, ld, (act_t*)q_out,
+  return tl_launch(rope_cache_write_kernel, grid, dim3(T >= 256 ? 128 : 32), 0, stream, qkv, ld, (act_t*)q_out,
                    (act_t*)k_pages, (act_t*)v_pages, token_pos, token_seq, seq_slot, page_table,
                    table_stride, inv_freq, style, nh, nkv, hd, per_block);
 }
