@@ -393,3 +393,38 @@ def test_attention_far_key_stands_out_in_every_kernel(kernel):
             for p_ in (last, last - 1, max(hot, 0)):     # rows that see the hot key, or just miss it
                 ref = attention_reference(q.cpu().view(n, nh, hd)[p_], pc.k[0], pc.v[0], p_, window, scale)
                 assert torch.allclose(got[p_], ref, **_attn_tol(dtype)), f"{kernel} window {window} hot {hot} row {p_}"
+
+
+@pytest.mark.parametrize("M", [1, 8, 64, 150, 300])
+def test_gemm_folds_the_norm_between_two_products(M):
+    """Producer: C += a @ w.T also leaves bf16(C * norm_weight) and per-tile sums of squares;
+    consumer: a product on that, scaled by 1/rms, equals the product on the normed stream."""
+    from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16
+    from torchless_rs_b200.parts.linear import NormCarry
+    g = GemmBf16.get()
+    H, K, N2, eps = 256, 512, 384, 1e-5
+    a = _rand((M, K), torch.bfloat16, 101)
+    w = _rand((H, K), torch.bfloat16, 102, 1.0 / math.sqrt(K))
+    nw = (1 + 0.1 * _rand((H,), torch.float32, 103)).to(torch.bfloat16)
+    stream = _rand((M, H), torch.float32, 104)
+    want_stream = stream.double() + a.double() @ w.double().T
+    carry = NormCarry(torch.zeros((M, H), dtype=torch.bfloat16, device=DEV),
+                      torch.zeros((M, (H + 127) // 128), dtype=torch.float32, device=DEV), H, eps)
+    assert g.run(a, w, stream, 1, emit=(nw, carry))
+    assert torch.allclose(stream.double(), want_stream, rtol=1e-4, atol=1e-4)
+    if not carry.valid:       # many tokens: the kernel does not fold (it was measured to gain nothing)
+        assert M > 128
+        return
+    assert torch.allclose(carry.xw.double(), want_stream * nw.double(), rtol=1e-2, atol=1e-2)
+    assert torch.allclose(carry.ss.double().sum(1), (want_stream ** 2).sum(1), rtol=1e-4)
+    w2 = _rand((2 * N2, H), torch.bfloat16, 105, 1.0 / math.sqrt(H))
+    normed = want_stream / torch.sqrt((want_stream ** 2).mean(1, keepdim=True) + eps) * nw.double()
+    ref = normed @ w2.double()[:N2].T
+    up = normed @ w2.double()[N2:].T
+    out = torch.empty((M, N2), dtype=torch.float32, device=DEV)
+    assert g.run(carry.xw, w2[:N2], out, 0, scaled=carry)
+    assert torch.allclose(out.double(), ref, rtol=2e-2, atol=2e-2)
+    act = torch.empty((M, N2), dtype=torch.bfloat16, device=DEV)
+    assert g.run(carry.xw, w2, act, 2, scaled=carry)
+    assert torch.allclose(act.double(), ref / (1 + torch.exp(-ref)) * up, rtol=3e-2, atol=3e-2)
+    assert g.take_error() == 0
