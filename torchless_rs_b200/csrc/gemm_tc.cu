@@ -715,7 +715,6 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   if (mode < 0 || mode > 3) return -1;
   const bool swiglu = mode == MODE_SWIGLU;
   int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-  if (M > 128 && getenv("TL_GEMM_BIG_BN")) bn = atoi(getenv("TL_GEMM_BIG_BN"));
   const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = (M + bn - 1) / bn;
   const long long tiles = (long long)n_tiles * m_tiles;
   const int kb_total = (K + TILE_K - 1) / TILE_K;
@@ -723,8 +722,7 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   const bool two_per_sm = bn <= 64;
   // small token tiles leave room for the blocks of the next kernel, which fetch their first
   // weight tiles while this kernel drains
-  const size_t big_budget = getenv("TL_GEMM_BIG_KB") ? (size_t)atoi(getenv("TL_GEMM_BIG_KB")) * 1024 : 224 * 1024;
-  const size_t budget = !two_per_sm ? big_budget : (!swiglu && bn <= 32) ? 80 * 1024 : 112 * 1024;
+  const size_t budget = !two_per_sm ? 224 * 1024 : (!swiglu && bn <= 32) ? 80 * 1024 : 112 * 1024;
   const long long slots = (long long)num_sms * (two_per_sm ? 2 : 1);
   int splits = 1;
   if (tiles < slots && two_per_sm) {
@@ -733,13 +731,12 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
     // keeps every block resident at once
     while (splits * 2 <= MAX_SPLITS && tiles * splits * 2 <= slots && splits * 2 <= kb_total / 2)
       splits *= 2;
-    if (getenv("TL_GEMM_SPLITS")) splits = atoi(getenv("TL_GEMM_SPLITS"));
   }
   int kb_per_split = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
   // many tokens: the persistent kernel with two accumulators (token tile 256, or 128 with
   // the SiLU-gate's two accumulators per tile)
-  const bool persistent = M > 128 && !ss_in && !getenv("TL_GEMM_NO_PERSISTENT");
+  const bool persistent = M > 128 && !ss_in;
   if (persistent) bn = swiglu ? 128 : 256;
   CUtensorMap tw, tx;
   if (!make_map(&tw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, TILE_N)) return -2;
