@@ -239,7 +239,7 @@ def test_attention_decode_bf16(nh, nkv, hd, window, use_tma):
     ws = Workspace(torch.device(DEV))
     qc = q.cpu().view(B, nh, hd)
     refs = [attention_reference(qc[b], pc.k[b], pc.v[b], lens[b] - 1, window, scale) for b in range(B)]
-    for n_splits in (1, 2, 3, 7, 40):
+    for n_splits in (1, 2, 3, 4, 7, 8, 40):
         out = torch.full((B, nh * hd), float("nan"), dtype=dtype, device=DEV)
         att.decode(q, pc.k_pages, pc.v_pages, out, seq_len, pc.seq_slot, pc.table, nh, nkv, window,
                    scale, n_splits, ws, use_tma=use_tma)

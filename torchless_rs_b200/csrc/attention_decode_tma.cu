@@ -13,6 +13,7 @@
 // Every wait on an mbarrier is bounded; when a bound is hit the block records a code in
 // tl_attn_tma_error and stops.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "attention_bf16_common.cuh"
 
@@ -87,6 +88,7 @@ template <bool HI>
 __global__ void __launch_bounds__(TD_WARPS * 32, 2)
 FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            const __nv_bfloat16* __restrict__ q, float* __restrict__ part,
+                           __nv_bfloat16* __restrict__ out,
                            const int* __restrict__ seq_len, const int* __restrict__ seq_slot,
                            const int* __restrict__ page_table, int table_stride, int nh, int nkv,
                            int window, float scale_log2, int n_splits) {
@@ -263,9 +265,13 @@ FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __gri
       acc += f * sm_o[(size_t)(w * 16 + r) * HEAD_DIM + d];
       l += f * sm_l[w * 16 + r];
     }
-    float* dst = part + (((size_t)b * nh + kvh * G + r) * n_splits + split) * PART_STRIDE;
-    dst[d] = acc;
-    if (d == 0) { dst[HEAD_DIM] = m; dst[HEAD_DIM + 1] = l; }
+    if (n_splits == 1) {   // nothing to merge: this is the result
+      out[((size_t)b * nh + kvh * G + r) * HEAD_DIM + d] = __float2bfloat16_rn(acc / l);
+    } else {
+      float* dst = part + (((size_t)b * nh + kvh * G + r) * n_splits + split) * PART_STRIDE;
+      dst[d] = acc;
+      if (d == 0) { dst[HEAD_DIM] = m; dst[HEAD_DIM + 1] = l; }
+    }
   }
 }
 
@@ -541,13 +547,13 @@ extern "C" int FN(tl_attn_decode_tma)(const void* q, const void* k_pages, const 
   int st;
   if (nh / nkv > 8)
     st = tl_launch(FN(attn_decode_tma_kernel)<true>, grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
-                   (const __nv_bfloat16*)q, part, seq_len, seq_slot, page_table, table_stride, nh, nkv,
-                   window, scale_log2, n_splits);
+                   (const __nv_bfloat16*)q, part, (__nv_bfloat16*)out, seq_len, seq_slot, page_table,
+                   table_stride, nh, nkv, window, scale_log2, n_splits);
   else
     st = tl_launch(FN(attn_decode_tma_kernel)<false>, grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
-                   (const __nv_bfloat16*)q, part, seq_len, seq_slot, page_table, table_stride, nh, nkv,
-                   window, scale_log2, n_splits);
-  if (st) return st;
+                   (const __nv_bfloat16*)q, part, (__nv_bfloat16*)out, seq_len, seq_slot, page_table,
+                   table_stride, nh, nkv, window, scale_log2, n_splits);
+  if (st || n_splits == 1) return st;   // a single split has written the result itself
   return tl_launch(FN(attn_decode_tma_combine_kernel), dim3(nh, B), dim3(HEAD_DIM), 0, stream,
                    (const float*)part, (__nv_bfloat16*)out, nh, n_splits);
 #endif
