@@ -320,10 +320,10 @@ def test_gemm_tensor_core(M, N, K):
     assert g.take_error() == 0
 
 
-@pytest.mark.parametrize("use_tma", [True, False])
+@pytest.mark.parametrize("variant", ["tc", "tma", "plain"])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, None), (8, 2, 128, 100), (4, 4, 64, 33),
                                                (3, 1, 32, None), (6, 3, 64, 64)])
-def test_attention_prefill_bf16(nh, nkv, hd, window, use_tma):
+def test_attention_prefill_bf16(nh, nkv, hd, window, variant):
     """Tensor-core prefill kernel: sequences from scratch and continuing ones, lengths
     around the 16-query warps, the 64-query tiles and the 32-key groups."""
     from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
@@ -342,7 +342,7 @@ def test_attention_prefill_bf16(nh, nkv, hd, window, use_tma):
     out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
     scale = 1 / math.sqrt(hd)
     att.prefill(q, pc.k_pages, pc.v_pages, out, seq_start, seq_len, pc.seq_slot, pc.table, B,
-                max(new), nh, nkv, window, scale, use_tma=use_tma)
+                max(new), nh, nkv, window, scale, variant=variant)
     assert att.take_error() == 0
     got = out.cpu().double().view(T, nh, hd)
     qc = q.cpu().view(T, nh, hd)
@@ -353,7 +353,8 @@ def test_attention_prefill_bf16(nh, nkv, hd, window, use_tma):
             assert torch.allclose(got[tkn], ref, **_attn_tol(dtype)), f"seq {b} pos {pos}"
 
 
-@pytest.mark.parametrize("kernel", ["prefill_bf16", "prefill_bf16_no_tma", "generic_bf16", "generic_f32"])
+@pytest.mark.parametrize("kernel", ["prefill_bf16_tc", "prefill_bf16_tma", "prefill_bf16_plain", "generic_bf16",
+                                    "generic_f32"])
 def test_attention_far_key_stands_out_in_every_kernel(kernel):
     """The same idea as for the decode kernel, for the kernels that take many queries: one
     key far back matches the last queries strongly; with a window it sits on the window's
@@ -385,7 +386,7 @@ def test_attention_far_key_stands_out_in_every_kernel(kernel):
                 AttentionBf16.get(hd).prefill(
                     q, pc.k_pages, pc.v_pages, out, torch.tensor([0, n], dtype=torch.int32, device=DEV),
                     torch.tensor([n], dtype=torch.int32, device=DEV), pc.seq_slot, pc.table, 1, n, nh, nkv,
-                    window, scale, use_tma=not kernel.endswith("no_tma"))
+                    window, scale, variant=kernel.rsplit("_", 1)[1])
             else:
                 _ops(dtype).attn_generic(q, pc.k_pages, pc.v_pages, out, pos, seq, pc.seq_slot, pc.table,
                                          nh, nkv, hd, window, scale)

@@ -19,7 +19,7 @@ TARGET_BLOCKS = 296   # 148 SMs x 2 resident blocks: one full wave measured best
 for _hd in FAST_HEAD_DIMS:
     build.register_library(f"attn_bf16_hd{_hd}",
                            ("attention_decode_bf16.cu", "attention_prefill_bf16.cu") +
-                           (("attention_decode_tma.cu",) if _hd % 64 == 0 else ()),
+                           (("attention_decode_tma.cu", "attention_prefill_tc.cu") if _hd % 64 == 0 else ()),
                            (f"-DHEAD_DIM={_hd}",))
     # the same kernels with a fixed scratch array inside the library, for callers that must
     # not allocate (see attention_decode_noalloc.h); nothing in this package loads it
@@ -62,12 +62,18 @@ class AttentionBf16:
                 self._decode_tma.restype = c_int
                 self._prefill_tma = getattr(self.lib, f"tl_attn_prefill_tma_hd{head_dim}")
                 self._prefill_tma.restype = c_int
+                self._prefill_tc = getattr(self.lib, f"tl_attn_prefill_tc_hd{head_dim}")
+                self._prefill_tc.restype = c_int
+                self._tc_error = getattr(self.lib, f"tl_attn_tc_take_error_hd{head_dim}")
+                self._tc_error.restype = c_int
                 self._tma_error = getattr(self.lib, f"tl_attn_tma_take_error_hd{head_dim}")
                 self._tma_error.restype = c_int
 
     def take_error(self) -> int:
         """Nonzero if a TMA kernel gave up on a bounded wait since the last call (synchronises)."""
-        return int(self._tma_error()) if getattr(self, "_decode_tma", None) is not None else 0
+        if getattr(self, "_decode_tma", None) is None:
+            return 0
+        return int(self._tma_error()) or int(self._tc_error())
 
     def decode(self, q, k_pages, v_pages, out, seq_len, seq_slot, page_table, nh, nkv, window,
                scale, n_splits, workspace, use_tma: bool = True) -> None:
@@ -94,14 +100,30 @@ class AttentionBf16:
                "attn_decode")
 
     def prefill(self, q, k_pages, v_pages, out, seq_start, seq_len, seq_slot, page_table, n_seqs,
-                max_new, nh, nkv, window, scale, use_tma: bool = True) -> None:
+                max_new, nh, nkv, window, scale, use_tma: bool = True, variant: str = "auto") -> None:
         """The new tokens of each sequence (packed, `seq_start` offsets) against the cache,
-        which already holds their keys and values."""
+        which already holds their keys and values.  `variant`: "tc" = tcgen05 kernel (head
+        sizes 64 and 128), "tma" = mma.sync on TMA-fed pages, "plain" = mma.sync on fragments
+        from global memory, "auto" = "tc" for steps with at least 128 new tokens, else "tma"."""
+        if not use_tma:
+            variant = "plain"
+        if variant == "auto":
+            variant = "tc" if max_new >= 128 else "tma"
         if self.lib is None:
             raise KernelError(f"no tensor-core prefill attention for head size {self.head_dim}")
         for t, n in ((q, "q"), (k_pages, "k pages"), (v_pages, "v pages"), (out, "out")):
             _need(t, torch.bfloat16, f"attn prefill {n}")
-        if getattr(self, "_decode_tma", None) is not None and use_tma:
+        if getattr(self, "_decode_tma", None) is not None and variant == "tc":
+            st = self._prefill_tc(_ptr(q), c_longlong(q.shape[0]), _ptr(k_pages), _ptr(v_pages),
+                                  c_longlong(k_pages.shape[0]), _ptr(out), _ptr(seq_start), _ptr(seq_len),
+                                  _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)),
+                                  c_int(n_seqs), c_int(max_new), c_int(nh), c_int(nkv), c_int(window or 0),
+                                  c_float(scale), _stream())
+            if st != -2:
+                _check(st, "attn_prefill_tc")
+                return
+            variant = "tma"
+        if getattr(self, "_decode_tma", None) is not None and variant == "tma":
             st = self._prefill_tma(_ptr(q), _ptr(k_pages), _ptr(v_pages), c_longlong(k_pages.shape[0]),
                                    _ptr(out), _ptr(seq_start), _ptr(seq_len), _ptr(seq_slot),
                                    _ptr(page_table), c_int(page_table.stride(0)), c_int(n_seqs),

@@ -52,7 +52,7 @@ __device__ __forceinline__ bool td_mbar_wait(uint64_t* bar, uint32_t parity, vol
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(td_smem_u32(bar)), "r"(parity)

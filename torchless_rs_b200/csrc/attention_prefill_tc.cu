@@ -1,0 +1,457 @@
+// Prefill attention of the bfloat16 path on the fifth-generation tensor cores.
+//
+// A block owns 128 consecutive queries of one head (the M of tcgen05.mma) and walks over
+// the cache pages that any of them can see.  Per page of 64 keys:
+//   S[128, 64]  = Q . K^T        tcgen05.mma, Q and the page's K slab in shared memory,
+//                                S in tensor memory
+//   softmax     four warps, one thread per query row: tcgen05.ld of the row, mask, running
+//               maximum and sum in 32-bit (no shuffles: a row lives in one thread), P
+//               rounded to bfloat16 into shared memory; O is rescaled in tensor memory only
+//               when some row's maximum moved
+//   O[128, hd] += P . V          tcgen05.mma, P from shared memory, the page's transposed V
+//                                slab as the K-major B operand
+// Pages come by TMA (three in flight).  Arithmetic as in attention_prefill_bf16.cu
+// (reference: src/model/modules/attention.rs:88-121, src/model/modules/flash_attention.rs:
+// 101-136, window of src/model/models/gpt_oss.rs:168-176).  Head sizes 64 and 128.
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the block records a code in
+// tl_attn_tc_error, stops, frees its tensor memory and returns.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "attention_bf16_common.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#define TC_Q 128                         // queries per block
+#define TC_STAGES 2                      // two blocks per SM: one block's products overlap the other's softmax
+#define TC_THREADS 192                   // warps 0-3 softmax, warp 4 TMA, warp 5 MMA
+#define TC_KSUB (HEAD_DIM / 64)
+#define TC_Q_BYTES (TC_Q * HEAD_DIM * 2)
+#define TC_K_BYTES (PAGE * HEAD_DIM * 2)
+#define TC_V_BYTES (HEAD_DIM * PAGE * 2)
+// P[128 queries, 64 keys] is as large as the K slab of a page when the head size is 128; it is then
+// written over that slab, which Q.K^T has finished with, and needs no buffer of its own
+#define TC_P_IN_K (HEAD_DIM == 128)
+#define TC_P_BYTES (TC_P_IN_K ? 0 : TC_Q * PAGE * 2)
+#define TC_STAGE_BYTES (TC_K_BYTES + TC_V_BYTES)
+#define TC_WAIT_LIMIT (1u << 22)
+#define TC_TMEM_COLS (HEAD_DIM == 128 ? 256 : 128)   // S (64 columns) then O (HEAD_DIM columns)
+
+__device__ int tl_attn_tc_error = 0;
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(tc_smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = code;
+  atomicCAS(&tl_attn_tc_error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tc_tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(tc_smem_u32(dst)), "l"(map), "r"(tc_smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major tile with 128-byte rows and the 128-byte swizzle: 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+__device__ __forceinline__ uint32_t tc_idesc(int n) {   // bf16 x bf16 -> f32, M = 128, both K-major
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(TC_THREADS)
+FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                           const __grid_constant__ CUtensorMap tm_v, __nv_bfloat16* __restrict__ out,
+                           const int* __restrict__ seq_start, const int* __restrict__ seq_len,
+                           const int* __restrict__ seq_slot, const int* __restrict__ page_table,
+                           int table_stride, int nh, int nkv, int window, float scale_log2) {
+  extern __shared__ uint8_t tc_smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;
+  uint8_t* p_s = q_s + TC_Q_BYTES;
+  uint8_t* kv_s = p_s + TC_P_BYTES;
+  uint64_t* q_full = (uint64_t*)(kv_s + TC_STAGES * TC_STAGE_BYTES);
+  uint64_t* kv_full = q_full + 1;
+  uint64_t* kv_empty = kv_full + TC_STAGES;
+  uint64_t* s_full = kv_empty + TC_STAGES;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* o_done = p_full + 1;
+  uint32_t* tmem_slot = (uint32_t*)(o_done + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tok0 = seq_start[b];
+  const int n_new = seq_start[b + 1] - tok0;
+  const int blk0 = blockIdx.x * TC_Q;
+  if (blk0 >= n_new) return;   // before any tensor memory is taken
+
+  if (threadIdx.x == 0) {
+    tc_mbar_init(q_full, 1);
+    for (int s = 0; s < TC_STAGES; ++s) { tc_mbar_init(&kv_full[s], 1); tc_mbar_init(&kv_empty[s], 1); }
+    tc_mbar_init(s_full, 1);
+    tc_mbar_init(p_full, 128);
+    tc_mbar_init(o_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)),
+                 "r"((uint32_t)TC_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + PAGE;   // S takes the first 64 columns
+
+  const int len = seq_len[b];
+  const int past = len - n_new;
+  const int kvh = h / (nh / nkv);
+  const int* table = page_table + (size_t)seq_slot[b] * table_stride;
+  const int rows = min(TC_Q, n_new - blk0);
+  const int blk_first = past + blk0, blk_last = past + blk0 + rows - 1;
+  const int blk_lo = (window > 0 && blk_first - window + 1 > 0) ? blk_first - window + 1 : 0;
+  const int ps = blk_lo / PAGE;
+  const int n_pg = blk_last / PAGE - ps + 1;
+
+  if (warp == 4 && lane == 0) {
+    // ---- TMA producer: the block's queries once, then the pages
+    tc_mbar_expect_tx(q_full, TC_Q_BYTES);
+#pragma unroll
+    for (int sub = 0; sub < TC_KSUB; ++sub)
+      tc_tma_load_2d(q_s + sub * (TC_Q * 128), &tm_q, q_full, h * HEAD_DIM + sub * 64, tok0 + blk0);
+    for (int i = 0; i < n_pg; ++i) {
+      const int s = i % TC_STAGES;
+      if (!tc_mbar_wait(&kv_empty[s], ((uint32_t)(i / TC_STAGES) & 1u) ^ 1u, abort_flag, 1)) break;
+      const int slab = table[ps + i] * nkv + kvh;
+      uint8_t* st = kv_s + (size_t)s * TC_STAGE_BYTES;
+      tc_mbar_expect_tx(&kv_full[s], TC_STAGE_BYTES);
+#pragma unroll
+      for (int sub = 0; sub < TC_KSUB; ++sub)
+        tc_tma_load_2d(st + sub * (PAGE * 128), &tm_k, &kv_full[s], sub * 64, slab * PAGE);
+      tc_tma_load_2d(st + TC_K_BYTES, &tm_v, &kv_full[s], 0, slab * HEAD_DIM);
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ---- MMA issuer
+    const uint32_t idesc_s = tc_idesc(PAGE), idesc_o = tc_idesc(HEAD_DIM);
+    const uint32_t qa = tc_smem_u32(q_s);
+    bool ok = tc_mbar_wait(q_full, 0, abort_flag, 2);
+    auto issue_pv = [&](int j) {   // O (+)= P(j) . V(j)
+      const uint32_t st_j = tc_smem_u32(kv_s + (size_t)(j % TC_STAGES) * TC_STAGE_BYTES);
+      const uint32_t va = st_j + TC_K_BYTES;
+      const uint32_t pa = TC_P_IN_K ? st_j : tc_smem_u32(p_s);
+#pragma unroll
+      for (int k = 0; k < PAGE / 16; ++k)
+        tc_umma(tmem_o, tc_desc(pa) + (uint64_t)(k * 2), tc_desc(va) + (uint64_t)(k * 2), idesc_o,
+                (j > 0 || k > 0) ? 1u : 0u);
+      tc_commit(&kv_empty[j % TC_STAGES]);   // the page's stage is free once these have read it
+      tc_commit(o_done);
+    };
+    for (int i = 0; i < n_pg && ok; ++i) {
+      const int s = i % TC_STAGES;
+      ok = tc_mbar_wait(&kv_full[s], (uint32_t)(i / TC_STAGES) & 1u, abort_flag, 3);
+      if (!ok) break;
+      if (i > 0) {
+        ok = tc_mbar_wait(p_full, (uint32_t)(i - 1) & 1u, abort_flag, 4);
+        if (!ok) break;
+        tc_fence_after();
+        issue_pv(i - 1);
+      }
+      tc_fence_after();
+      const uint32_t ka = tc_smem_u32(kv_s + (size_t)s * TC_STAGE_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < HEAD_DIM / 16; ++kk) {
+        const uint32_t sub = kk >> 2, within = (kk & 3) * 2;   // 32 bytes per step inside a 64-column box
+        tc_umma(tmem_base, tc_desc(qa + sub * (TC_Q * 128)) + within, tc_desc(ka + sub * (PAGE * 128)) + within,
+                idesc_s, kk > 0 ? 1u : 0u);
+      }
+      tc_commit(s_full);
+    }
+    if (ok) ok = tc_mbar_wait(p_full, (uint32_t)(n_pg - 1) & 1u, abort_flag, 4);
+    if (ok) {
+      tc_fence_after();
+      issue_pv(n_pg - 1);
+    }
+  } else if (warp < 4) {
+    // ---- softmax: one thread per query row
+    const int r = threadIdx.x;
+    const bool valid_row = r < rows;
+    const int pos = past + blk0 + min(r, rows - 1);
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const uint32_t t_s = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_o = tmem_o + ((uint32_t)(warp * 32) << 16);
+    float m = -INFINITY, l = 0.0f;
+    bool ok = true;
+    for (int i = 0; i < n_pg; ++i) {
+      ok = tc_mbar_wait(s_full, (uint32_t)i & 1u, abort_flag, 5);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sa[32], sb[32];
+      tc_ld32(t_s, sa);
+      tc_ld32(t_s + 32, sb);
+      tc_wait_ld();
+      const int key0 = (ps + i) * PAGE;
+      // a page that every row of this warp sees whole needs no mask (all but the pages on the
+      // diagonal and at a window's edge)
+      const bool whole = __all_sync(0xffffffffu, valid_row && key0 >= lo && key0 + PAGE - 1 <= pos);
+      float mx = -INFINITY;
+      if (whole) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
+        mx *= scale_log2;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int ka_ = key0 + j, kb_ = key0 + 32 + j;
+          const float va = (valid_row && ka_ >= lo && ka_ <= pos) ? __uint_as_float(sa[j]) : -INFINITY;
+          const float vb = (valid_row && kb_ >= lo && kb_ <= pos) ? __uint_as_float(sb[j]) : -INFINITY;
+          sa[j] = __float_as_uint(va);
+          sb[j] = __float_as_uint(vb);
+          mx = fmaxf(mx, fmaxf(va, vb));
+        }
+        mx *= scale_log2;   // the scale is positive; -inf stays -inf
+      }
+      // `m` is the reference of the exponentials, not the exact running maximum: it moves only
+      // when a score exceeds it by more than 2^8, so that O in tensor memory is rarely rescaled;
+      // until then p may be as large as 256, which bfloat16 and the 32-bit sums hold with ease
+      const float m_new = (mx > m + 8.0f || m == -INFINITY) ? fmaxf(m, mx) : m;
+      const float ref = m_new == -INFINITY ? 0.0f : m_new;
+      const float alpha = exp2f(m - ref);
+      m = m_new;
+      float sum = 0.0f;
+      uint32_t pk[32];   // the row of P as bfloat16 pairs: 64 keys = 128 bytes
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float p0 = exp2f(fmaf(__uint_as_float(sa[2 * j]), scale_log2, -ref));
+        const float p1 = exp2f(fmaf(__uint_as_float(sa[2 * j + 1]), scale_log2, -ref));
+        const float p2 = exp2f(fmaf(__uint_as_float(sb[2 * j]), scale_log2, -ref));
+        const float p3 = exp2f(fmaf(__uint_as_float(sb[2 * j + 1]), scale_log2, -ref));
+        sum += (p0 + p1) + (p2 + p3);
+        pk[j] = pack_bf16(p0, p1);
+        pk[16 + j] = pack_bf16(p2, p3);
+      }
+      l = l * alpha + sum;
+      if (i > 0) {
+        // P(i-1) . V(i-1) has finished: O is stable and the P tile may be written again
+        ok = tc_mbar_wait(o_done, (uint32_t)(i - 1) & 1u, abort_flag, 6);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {   // some row's reference moved: rescale O
+#pragma unroll
+          for (int c = 0; c < HEAD_DIM; c += 32) {
+            uint32_t ov[32];
+            tc_ld32(t_o + c, ov);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
+            tc_st32(t_o + c, ov);
+          }
+          tc_wait_st();
+        }
+      }
+      // row r of the P tile: 8 chunks of 16 bytes, chunk c at (c ^ (r & 7))
+      const uint32_t prow = (TC_P_IN_K ? tc_smem_u32(kv_s + (size_t)(i % TC_STAGES) * TC_STAGE_BYTES)
+                                       : tc_smem_u32(p_s)) + (uint32_t)r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (uint32_t)((c ^ (r & 7)) << 4)),
+                     "r"(pk[4 * c]), "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
+                     : "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core's reads
+      tc_fence_before();
+      tc_mbar_arrive(p_full);
+    }
+    if (ok) ok = tc_mbar_wait(o_done, (uint32_t)(n_pg - 1) & 1u, abort_flag, 7);
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      __nv_bfloat16* orow = out + ((size_t)(tok0 + blk0 + r) * nh + h) * HEAD_DIM;
+#pragma unroll
+      for (int c = 0; c < HEAD_DIM; c += 32) {
+        uint32_t ov[32];
+        tc_ld32(t_o + c, ov);
+        tc_wait_ld();
+        if (valid_row) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(ov[j]) * inv, __uint_as_float(ov[j + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(ov[j + 2]) * inv, __uint_as_float(ov[j + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(ov[j + 4]) * inv, __uint_as_float(ov[j + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(ov[j + 6]) * inv, __uint_as_float(ov[j + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c + j) = w;
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TC_TMEM_COLS)
+                 : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*TcEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+
+static TcEncodeFn tc_encode_fn() {
+  static TcEncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (TcEncodeFn)p;
+  });
+  return fn;
+}
+
+// rows x cols bfloat16, contiguous rows; boxes of 64 columns (128 bytes) x box_rows, 128-byte swizzle
+static bool tc_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
+  typedef std::tuple<const void*, long long, long long, int> Key;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key(ptr, rows, cols, box_rows);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *map = it->second; return true; }
+  TcEncodeFn fn = tc_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = m;
+  *map = m;
+  return true;
+}
+
+// q, out [T, nh*HEAD_DIM]; max_new = the most new tokens any sequence of the step has.
+// Returns -2 for sizes this kernel does not take.
+extern "C" int FN(tl_attn_prefill_tc)(const void* q, long long T, const void* k_pages, const void* v_pages,
+                                      long long n_pages, void* out, const int* seq_start,
+                                      const int* seq_len, const int* seq_slot, const int* page_table,
+                                      int table_stride, int B, int max_new, int nh, int nkv, int window,
+                                      float scale, cudaStream_t stream) {
+#if HEAD_DIM % 64 != 0
+  return -2;
+#else
+  if (B <= 0 || max_new <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh > 65535 || B > 65535 || ((uintptr_t)q & 15) ||
+      ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+    return -2;
+  CUtensorMap tq, tk, tv;
+  if (!tc_make_map(&tq, q, T, (long long)nh * HEAD_DIM, TC_Q)) return -2;
+  if (!tc_make_map(&tk, k_pages, n_pages * nkv * PAGE, HEAD_DIM, PAGE)) return -2;
+  if (!tc_make_map(&tv, v_pages, n_pages * nkv * HEAD_DIM, PAGE, HEAD_DIM)) return -2;
+  const size_t smem = 1024 + TC_Q_BYTES + TC_P_BYTES + (size_t)TC_STAGES * TC_STAGE_BYTES + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(FN(attn_prefill_tc_kernel),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_new + TC_Q - 1) / TC_Q, nh, B);
+  return tl_launch(FN(attn_prefill_tc_kernel), grid, dim3(TC_THREADS), smem, stream, tq, tk, tv,
+                   (__nv_bfloat16*)out, seq_start, seq_len, seq_slot, page_table, table_stride, nh, nkv,
+                   window, scale * 1.4426950408889634f);
+#endif
+}
+
+extern "C" int FN(tl_attn_tc_take_error)() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, tl_attn_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(tl_attn_tc_error, &zero, sizeof(int));
+  return v;
+}

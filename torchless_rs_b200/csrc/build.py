@@ -43,7 +43,9 @@ class BuildError(RuntimeError):
 
 
 def register_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()) -> None:
-    LIBRARIES[name] = (tuple(sources), tuple(defines))
+    # $TL_NVCC_FLAGS: extra compiler flags for experiments (they enter the library's hash)
+    extra = tuple(os.environ.get("TL_NVCC_FLAGS", "").split())
+    LIBRARIES[name] = (tuple(sources), tuple(defines) + extra)
 
 
 def find_nvcc() -> str:

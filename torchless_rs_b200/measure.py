@@ -90,9 +90,11 @@ def attn_prefill(T: int, iters: int, nh=32, nkv=8, hd=128) -> None:
     lens = torch.tensor([T], dtype=torch.int32, device="cuda")
     q = torch.randn((T, nh * hd), device="cuda", dtype=torch.bfloat16)
     out = torch.empty_like(q)
-    us = _time(lambda: att.prefill(q, kp, vp, out, start, lens, slot, table, 1, T, nh, nkv, None,
-                                   1 / math.sqrt(hd)), iters)
-    print(f"attn-prefill tokens={T}: {us:.2f} us, {2.0 * nh * hd * T * T / us / 1e6:.1f} TFLOP/s (causal half counted)")
+    for variant in ("tc", "tma"):
+        us = _time(lambda: att.prefill(q, kp, vp, out, start, lens, slot, table, 1, T, nh, nkv, None,
+                                       1 / math.sqrt(hd), variant=variant), iters)
+        print(f"attn-prefill tokens={T} kernel={variant}: {us:.2f} us, "
+              f"{2.0 * nh * hd * T * T / us / 1e6:.1f} TFLOP/s (causal half counted), error word {att.take_error()}")
 
 
 def main() -> None:
