@@ -156,7 +156,8 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
   pdl_launch_dependents();
   const int tok0 = seq_start[b];
   const int n_new = seq_start[b + 1] - tok0;
-  const int blk0 = blockIdx.x * TC_Q;
+  // the last queries of a sequence see the most keys: their blocks come first in the grid
+  const int blk0 = (int)(gridDim.x - 1 - blockIdx.x) * TC_Q;
   if (blk0 >= n_new) return;   // before any tensor memory is taken
 
   if (threadIdx.x == 0) {
