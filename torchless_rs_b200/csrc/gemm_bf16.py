@@ -2,6 +2,7 @@
 returns False for a shape it does not take; the caller then uses the CUDA-core kernel."""
 from __future__ import annotations
 
+import ctypes
 from ctypes import byref, c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -10,6 +11,15 @@ from . import build
 from .ops import KernelError, _check, _ptr, _stream
 
 build.register_library("gemm_tc", ("gemm_tc.cu",), ())
+
+
+class RopeArgs(ctypes.Structure):
+    """Mirror of TlRopeArgs in gemm_tc.cu: what the q/k/v product needs to rotate q and k and
+    write k and v into the cache pages itself."""
+    _fields_ = [("q_out", c_void_p), ("k_pages", c_void_p), ("v_pages", c_void_p),
+                ("token_pos", c_void_p), ("token_seq", c_void_p), ("seq_slot", c_void_p),
+                ("page_table", c_void_p), ("inv_freq", c_void_p),
+                ("table_stride", c_int), ("style", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int)]
 
 
 class GemmBf16:
@@ -34,12 +44,15 @@ class GemmBf16:
         return self._scratch[key]
 
     def run(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int,
-            scaled=None, emit=None) -> bool:
+            scaled=None, emit=None, rope: "RopeArgs" = None) -> bool:
         """out (op)= a @ w.T.  Returns False for shapes this kernel does not take.
 
         `scaled`: a `NormCarry` whose `xw` is `a`; outputs are scaled by each row's
         1/rms from its partial sums.  `emit`: (norm weight, NormCarry) for mode 1: if the
-        kernel can, it fills the carry with the next norm's input and sets `carry.valid`."""
+        kernel can, it fills the carry with the next norm's input and sets `carry.valid`.
+        `rope`: for the q/k/v product (mode 0): if the kernel can, it rotates and writes q, k
+        and v itself instead of `out`; `self.rope_applied` says whether it did."""
+        self.rope_applied = False
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             return False
         if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
@@ -52,6 +65,7 @@ class GemmBf16:
                               f"out {tuple(out.shape)} {out.dtype} mode {mode}")
         sms = self._scratch_for(a.device)
         emitted = c_int(0)
+        applied = c_int(0)
         ss_in = scaled.ss if scaled is not None else None
         nw, carry = emit if emit is not None else (None, None)
         st = self.lib.tl_gemm_tc(
@@ -62,12 +76,14 @@ class GemmBf16:
             c_float(scaled.eps if scaled is not None else 0.0),
             _ptr(carry.xw if carry is not None else None), _ptr(nw),
             c_int(1 if (nw is not None and nw.dtype == torch.float32) else 0),
-            _ptr(carry.ss if carry is not None else None), byref(emitted), _stream())
+            _ptr(carry.ss if carry is not None else None), byref(emitted),
+            byref(rope) if rope is not None else c_void_p(0), byref(applied), _stream())
         if st == -2:
             return False
         _check(st, "gemm_tc")
         if carry is not None:
             carry.valid = bool(emitted.value)
+        self.rope_applied = bool(applied.value)
         return True
 
     def take_error(self) -> int:

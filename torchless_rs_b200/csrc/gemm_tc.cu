@@ -185,6 +185,17 @@ struct GemmArgs {
   const void* nw;           // that weight [N]
   int nw_is_f32;
   float* ss_out;            // [M, tiles of N] partial sums of squares of the new C
+  // Rotation and cache write folded into the q/k/v product (K split only): the product's
+  // columns are query heads, then key heads, then value heads of `hd` columns each.
+  int rope_on, rope_style, rope_nh, rope_nkv, rope_hd, rope_table_stride;
+  __nv_bfloat16* rope_q;    // [M, nh * hd]
+  __nv_bfloat16* rope_k;    // key pages [pages, nkv, 64, hd]
+  __nv_bfloat16* rope_v;    // value pages [pages, nkv, hd, 64]
+  const int* rope_pos;      // [M] position of each token
+  const int* rope_seq;      // [M] batch row of each token
+  const int* rope_slot;     // cache slot of each batch row
+  const int* rope_table;    // page table
+  const float* rope_inv_freq;   // [hd / 2] or null
 };
 
 // 1 / sqrt(mean(x^2) + eps) of input row m from the partial sums the producer left.
@@ -364,6 +375,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       // partials of every split) are in flight together
       for (int cb = rank; cb < cols; cb += 8 * splits) {
         float v[8], uu[8], prev[8];
+        // with the rotation folded in, `uu` holds the partner of the pair (same token, the
+        // column that turns together with this one)
+        const int rope_half = args.rope_hd >> 1;
+        const int prow = args.rope_on ? (args.rope_style == 0 ? (row ^ rope_half) : (row ^ 1)) : row;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           const int c = cb + q * splits;
@@ -377,6 +392,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             for (int sp = 0; sp < splits; ++sp) {
               v[q] += ld_remote_f32(red_s + (uint32_t)(c * TILE_N + row) * 4u, (uint32_t)sp);
               if (SWIGLU) uu[q] += ld_remote_f32(red_s + (uint32_t)((BN + c) * TILE_N + row) * 4u, (uint32_t)sp);
+              else if (args.rope_on) uu[q] += ld_remote_f32(red_s + (uint32_t)(c * TILE_N + prow) * 4u, (uint32_t)sp);
             }
           }
         }
@@ -385,11 +401,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           const int c = cb + q * splits;
           if (c >= cols) break;
           float val = v[q], up = uu[q];
-          if (args.ss_in) { val *= rinv_c[c]; up *= rinv_c[c]; }
+          if (args.ss_in) { val *= rinv_c[c]; up *= rinv_c[c]; }   // `up` may be the rotation partner
           const size_t idx = (size_t)(m0 + c) * args.ldc + n;
           float sq = 0.0f;
           if (live) {
             if (SWIGLU) ((__nv_bfloat16*)args.C)[idx] = __float2bfloat16_rn(silu_f(val) * up);
+            else if (args.rope_on) {
+              // this column is dimension d of head `head`; rotate q and k at the token's position
+              // (angle, sine and cosine in 32-bit) and write q, or k and v into the token's page
+              const int hd = args.rope_hd, head = n / hd, d = n - head * hd, m_tok = m0 + c;
+              const int pos = args.rope_pos[m_tok];
+              float res = val;
+              if (head < args.rope_nh + args.rope_nkv && args.rope_inv_freq) {
+                const bool first = args.rope_style == 0 ? d < rope_half : (d & 1) == 0;
+                const int i = args.rope_style == 0 ? (first ? d : d - rope_half) : d >> 1;
+                float sn, cs;
+                sincosf((float)pos * args.rope_inv_freq[i], &sn, &cs);
+                res = first ? val * cs - up * sn : up * sn + val * cs;
+              }
+              if (head < args.rope_nh) {
+                args.rope_q[(size_t)m_tok * args.rope_nh * hd + n] = __float2bfloat16_rn(res);
+              } else {
+                const int page = args.rope_table[(size_t)args.rope_slot[args.rope_seq[m_tok]] * args.rope_table_stride +
+                                                 pos / 64];
+                if (page >= 0) {
+                  const bool is_k = head < args.rope_nh + args.rope_nkv;
+                  const int kvh = head - args.rope_nh - (is_k ? 0 : args.rope_nkv);
+                  const size_t base = ((size_t)page * args.rope_nkv + kvh) * (size_t)(64 * hd);
+                  if (is_k) args.rope_k[base + (size_t)(pos % 64) * hd + d] = __float2bfloat16_rn(res);
+                  else args.rope_v[base + (size_t)d * 64 + (pos % 64)] = __float2bfloat16_rn(res);
+                }
+              }
+            }
             else if (args.mode == MODE_STORE_F32) ((float*)args.C)[idx] = val;
             else if (accum) {
               const float cn = prev[q] + val;
@@ -695,6 +738,14 @@ static int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, GemmA
 
 #define MAX_SPLITS 8   // portable cluster size
 
+// What the caller passes to have rotation and cache write done by the q/k/v product.
+struct TlRopeArgs {
+  void* q_out; void* k_pages; void* v_pages;
+  const int* token_pos; const int* token_seq; const int* seq_slot; const int* page_table;
+  const float* inv_freq;
+  int table_stride, style, nh, nkv, hd;
+};
+
 // Returns 0, a CUDA error, or -2 when these sizes or alignments are not taken (the
 // caller then uses the CUDA-core kernel).  N counts output columns; in mode 2 W has 2N rows.
 //
@@ -704,11 +755,18 @@ static int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, GemmA
 // sets *emitted = 1; otherwise *emitted = 0 and the caller runs the norm kernel.  Consumer
 // side: with `ss_in` given, X is such an xw and every output is scaled by
 // 1 / sqrt(sum_t ss_in[m, t] / norm_h + eps_in) before the mode's operation.
+//
+// `rope` (a TlRopeArgs, mode 0, K split only): C is not written; instead the columns, read as
+// query, key and value heads, are rotated at each token's position and written to q_out and
+// into the token's cache page, and *rope_applied = 1.  Otherwise *rope_applied = 0 and the
+// caller runs the rotation kernel on C.
 extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* C, int ldc, int M,
                           int N, int K, int mode, int num_sms, const float* ss_in, int ss_in_tiles,
                           int norm_h, float eps_in, void* xw_out, const void* nw, int nw_is_f32,
-                          float* ss_out, int* emitted, cudaStream_t stream) {
+                          float* ss_out, int* emitted, const void* rope, int* rope_applied,
+                          cudaStream_t stream) {
   if (emitted) *emitted = 0;
+  if (rope_applied) *rope_applied = 0;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
     return -2;
@@ -749,6 +807,22 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   a.xw_out = emit ? (__nv_bfloat16*)xw_out : nullptr;
   a.nw = nw; a.nw_is_f32 = nw_is_f32; a.ss_out = emit ? ss_out : nullptr;
   if (emitted) *emitted = emit ? 1 : 0;
+  a.rope_on = 0;
+  if (rope && mode == MODE_STORE_F32 && splits > 1) {
+    const TlRopeArgs* r = (const TlRopeArgs*)rope;
+    // measured: a gain for a handful of tokens, a loss from a few dozen on (every thread then
+    // computes many sines and reads every partial twice)
+    const bool fits = (r->hd == 32 || r->hd == 64 || r->hd == 128) && N == (r->nh + 2 * r->nkv) * r->hd &&
+                      M <= 16;
+    if (fits) {
+      a.rope_on = 1; a.rope_style = r->style; a.rope_nh = r->nh; a.rope_nkv = r->nkv; a.rope_hd = r->hd;
+      a.rope_table_stride = r->table_stride;
+      a.rope_q = (__nv_bfloat16*)r->q_out; a.rope_k = (__nv_bfloat16*)r->k_pages;
+      a.rope_v = (__nv_bfloat16*)r->v_pages; a.rope_pos = r->token_pos; a.rope_seq = r->token_seq;
+      a.rope_slot = r->seq_slot; a.rope_table = r->page_table; a.rope_inv_freq = r->inv_freq;
+      if (rope_applied) *rope_applied = 1;
+    }
+  }
   if (persistent)
     return swiglu ? launch_persistent<128, true>(tw, tx, a, num_sms, stream)
                   : launch_persistent<256, false>(tw, tx, a, num_sms, stream);

@@ -94,15 +94,25 @@ class Attention:
         T = residual.shape[0]
         c = self.cache
         qkv = ws.get("attn_qkv", (T, self.qkv_cols), torch.float32)
-        self.matmul(xn, self.w_qkv, qkv, ops.MODE_STORE_F32)
         q = ws.get("attn_q", (T, self.nh * self.hd), rt.act_dtype)
         pos = self.position
-        rt.ops.rope_cache_write(
-            qkv, q, c.k_pages if self.own_cache else None, c.v_pages if self.own_cache else None,
-            batch.token_pos, batch.token_seq, batch.seq_slot,
-            c.page_table if self.own_cache else None,
-            pos.inv_freq if pos is not None else None, pos.style if pos is not None else 0,
-            self.nh, self.nkv, self.hd)
+        rope = None
+        if self.fast is not None and self.own_cache:
+            # the product may rotate and write q, k and v itself (it does when K is split)
+            from ..csrc.gemm_bf16 import RopeArgs
+            rope = RopeArgs(q.data_ptr(), c.k_pages.data_ptr(), c.v_pages.data_ptr(),
+                            batch.token_pos.data_ptr(), batch.token_seq.data_ptr(),
+                            batch.seq_slot.data_ptr(), c.page_table.data_ptr(),
+                            pos.inv_freq.data_ptr() if pos is not None else None,
+                            c.page_table.stride(0), pos.style if pos is not None else 0,
+                            self.nh, self.nkv, self.hd)
+        if not self.matmul(xn, self.w_qkv, qkv, ops.MODE_STORE_F32, rope=rope):
+            rt.ops.rope_cache_write(
+                qkv, q, c.k_pages if self.own_cache else None, c.v_pages if self.own_cache else None,
+                batch.token_pos, batch.token_seq, batch.seq_slot,
+                c.page_table if self.own_cache else None,
+                pos.inv_freq if pos is not None else None, pos.style if pos is not None else 0,
+                self.nh, self.nkv, self.hd)
         out = ws.get("attn_out", (T, self.nh * self.hd), rt.act_dtype)
         done = False
         if self.fast is not None:

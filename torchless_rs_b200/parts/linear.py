@@ -40,16 +40,19 @@ class Matmul:
             from ..csrc import gemm_bf16
             self.fast = gemm_bf16.GemmBf16.get()
 
-    def __call__(self, a, w: torch.Tensor, out: torch.Tensor, mode: int, emit=None) -> None:
+    def __call__(self, a, w: torch.Tensor, out: torch.Tensor, mode: int, emit=None, rope=None) -> bool:
         """`a` is an activation tensor or a `NormCarry`.  `emit` = (norm weight, NormCarry)
-        asks the product (mode 1) to prepare the next norm's input if it can."""
+        asks the product (mode 1) to prepare the next norm's input if it can.  `rope` (a
+        `gemm_bf16.RopeArgs`) asks the q/k/v product to rotate and write q, k and v itself;
+        the return value says whether it did (then `out` was not written)."""
         scaled = a if isinstance(a, NormCarry) else None
         if scaled is not None:
-            if self.fast is None or not self.fast.run(scaled.xw, w, out, mode, scaled=scaled):
+            if self.fast is None or not self.fast.run(scaled.xw, w, out, mode, scaled=scaled, rope=rope):
                 raise ops.KernelError("a folded norm reached a product that cannot apply it")
-            return
+            return self.fast.rope_applied
         if emit is not None:
             emit[1].valid = False
-        if self.fast is not None and self.fast.run(a, w, out, mode, emit=emit):
-            return
+        if self.fast is not None and self.fast.run(a, w, out, mode, emit=emit, rope=rope):
+            return self.fast.rope_applied
         self.rt.ops.gemm_generic(a, w, out, mode)
+        return False
