@@ -24,7 +24,7 @@ import time
 _ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, _ROOT)
 
-# BASELINE.json configs[2]
+# the sizes of Mistral-7B-v0.1 (the benchmark's third configuration)
 MISTRAL_7B = dict(
     architectures=["MistralForCausalLM"], model_type="mistral", num_hidden_layers=32,
     hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
