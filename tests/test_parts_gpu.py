@@ -293,3 +293,147 @@ def test_toy_mixer_with_state(dtype):
             bound = 5e-5 + 1e-4 * np.abs(ref).max() if dtype == torch.float32 else 2.5e-2 * np.abs(ref).max()
             assert np.abs(g - ref).max() < bound, f"round {round_} request {i}"
     assert eng.cache.slots.held_count == 0
+
+
+# ---------------------------------------------------------------------------
+# a toy feed-forward with routing and another position encoding, defined here
+# ---------------------------------------------------------------------------
+def _register_toy_routed_ffn():
+    from torchless_rs_b200.parts import register_feed_forward
+    from torchless_rs_b200.weights import TensorSpec
+
+    @register_feed_forward("toy_routed")
+    class ToyRouted:
+        """Router logits in 32-bit, the best expert per token, experts y = W2 relu(W1 x)."""
+
+        def __init__(self, spec, prefix, rt):
+            p = spec.params
+            self.h, self.e, self.w = p["hidden_size"], p["experts"], p["width"]
+            self.prefix, self.rt = prefix, rt
+
+        @classmethod
+        def expected_tensors(cls, spec, prefix):
+            h, e, w = spec.params["hidden_size"], spec.params["experts"], spec.params["width"]
+            t = {f"{prefix}.router.weight": TensorSpec((e, h))}
+            for i in range(e):
+                t[f"{prefix}.experts.{i}.w1.weight"] = TensorSpec((w, h))
+                t[f"{prefix}.experts.{i}.w2.weight"] = TensorSpec((h, w))
+            return t
+
+        def load(self, weights):
+            dev = self.rt.device
+            self.router = weights[f"{self.prefix}.router.weight"].float().to(dev)
+            self.w1 = [weights[f"{self.prefix}.experts.{i}.w1.weight"].float().to(dev) for i in range(self.e)]
+            self.w2 = [weights[f"{self.prefix}.experts.{i}.w2.weight"].float().to(dev) for i in range(self.e)]
+
+        def forward(self, xn, residual, batch):
+            x = xn.float()
+            choice = (x @ self.router.T).argmax(-1)
+            for i in range(self.e):
+                rows = (choice == i).nonzero().flatten()
+                if rows.numel():
+                    residual[rows] += torch.relu(x[rows] @ self.w1[i].T) @ self.w2[i].T
+    return ToyRouted
+
+
+def _register_interleaved_rope():
+    from torchless_rs_b200.parts import register_position
+    from torchless_rs_b200.parts.position import RotaryHalfSplit, STYLE_INTERLEAVED
+
+    @register_position("rope_interleaved_test")
+    class RotaryInterleaved(RotaryHalfSplit):
+        """The same angles, but dimension 2i turns with dimension 2i + 1."""
+        style = STYLE_INTERLEAVED
+    return RotaryInterleaved
+
+
+def _rope_interleaved(x, cos, sin):
+    a, b = x[..., 0::2], x[..., 1::2]
+    out = np.empty_like(x)
+    out[..., 0::2] = a * cos[:, None, :] - b * sin[:, None, :]
+    out[..., 1::2] = a * sin[:, None, :] + b * cos[:, None, :]
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_routed_feed_forward_and_another_position_encoding(dtype):
+    """Layer 0: attention with interleaved rotary pairs and the package's SwiGLU; layer 1: the
+    package's attention and a routed feed-forward defined here.  Whole prompts, then token
+    by token in a batch of two."""
+    from dataclasses import replace
+    from tiny import TINY_D
+    from torchless_rs_b200.config import ModelSpec, PartSpec, config_from_dict
+    _register_toy_routed_ffn()
+    _register_interleaved_rope()
+    cfg = config_from_dict(dict(TINY_D, num_hidden_layers=2, sliding_window=None))
+    base = cfg.model_spec()
+    layers = list(base.layers)
+    layers[0] = replace(layers[0], position=PartSpec("rope_interleaved_test", dict(layers[0].position.params)))
+    layers[1] = replace(layers[1], feed_forward=PartSpec("toy_routed", {"hidden_size": cfg.hidden_size,
+                                                                         "experts": 3, "width": 40}))
+    spec = ModelSpec(base.hidden_size, base.vocab_size, base.embedding_name, base.head_name, False,
+                     base.final_norm, base.final_norm_prefix, tuple(layers), base.order)
+    eng, wn = _engine(spec, 13, dtype)
+
+    def reference(toks):
+        n = len(toks)
+        pos = np.arange(n)
+        h = plain.embedding(wn["model.embed_tokens.weight"], toks)
+        # layer 0 by hand: interleaved rotation
+        lw = {k[len("model.layers.0."):]: v for k, v in wn.items() if k.startswith("model.layers.0.")}
+        x = plain.rmsnorm(h, lw["input_layernorm.weight"], cfg.rms_norm_eps)
+        nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        cos, sin = plain.rope_cos_sin(plain.rope_inv_freq(hd, cfg.rope_theta), pos)
+        q = _rope_interleaved((x @ lw["self_attn.q_proj.weight"].T).reshape(n, nh, hd), cos, sin)
+        k = _rope_interleaved((x @ lw["self_attn.k_proj.weight"].T).reshape(n, nkv, hd), cos, sin)
+        v = (x @ lw["self_attn.v_proj.weight"].T).reshape(n, nkv, hd)
+        h = h + plain.attention(q, k, v, None).reshape(n, nh * hd) @ lw["self_attn.o_proj.weight"].T
+        h = h + plain.swiglu(plain.rmsnorm(h, lw["post_attention_layernorm.weight"], cfg.rms_norm_eps),
+                             lw["mlp.gate_proj.weight"], lw["mlp.up_proj.weight"], lw["mlp.down_proj.weight"])
+        # layer 1: plain attention, then the routed feed-forward
+        lw = {k[len("model.layers.1."):]: v for k, v in wn.items() if k.startswith("model.layers.1.")}
+        a, _ = plain.attention_mixer(plain.rmsnorm(h, lw["input_layernorm.weight"], cfg.rms_norm_eps),
+                                     lw["self_attn.q_proj.weight"], lw["self_attn.k_proj.weight"],
+                                     lw["self_attn.v_proj.weight"], lw["self_attn.o_proj.weight"], pos, nh, nkv,
+                                     hd, cfg.rope_theta, None)
+        h = h + a
+        x = plain.rmsnorm(h, lw["post_attention_layernorm.weight"], cfg.rms_norm_eps)
+        if dtype == torch.bfloat16:      # the engine's norm output is rounded before the router sees it
+            x = torch.from_numpy(x).to(torch.bfloat16).float().numpy()
+        logits = x @ lw["mlp.router.weight"].T
+        choice = logits.argmax(-1)
+        margin = np.sort(logits, -1)
+        sure = (margin[:, -1] - margin[:, -2]) > 1e-3 * np.abs(logits).max()
+        out = np.zeros_like(h)
+        for i in range(n):
+            e = choice[i]
+            out[i] = np.maximum(x[i] @ lw[f"mlp.experts.{e}.w1.weight"].T, 0) @ lw[f"mlp.experts.{e}.w2.weight"].T
+        h = h + out
+        return plain.rmsnorm(h, wn["model.norm.weight"], cfg.rms_norm_eps) @ wn["lm_head.weight"].T, sure
+
+    rng = np.random.default_rng(5)
+    reqs = [[int(t) for t in rng.integers(0, cfg.vocab_size, n)] for n in (40, 17)]
+    slots = eng.start_sequences(2)
+    pre = [30, 5]
+    out = eng.step(slots, [r[:p] for r, p in zip(reqs, pre)], "all").cpu().numpy().copy()
+    got = [[out[:30]], [out[30:35]]]
+    fed, live = list(pre), [0, 1]
+    while live:
+        done = [i for i in live if fed[i] >= len(reqs[i])]
+        if done:
+            eng.end_sequences([slots[i] for i in done])
+            live = [i for i in live if i not in done]
+            continue
+        out = eng.step([slots[i] for i in live], [[reqs[i][fed[i]]] for i in live], "last").cpu().numpy().copy()
+        for j, i in enumerate(live):
+            got[i].append(out[j:j + 1])
+            fed[i] += 1
+    for i, r in enumerate(reqs):
+        ref, sure = reference(r)
+        g = np.concatenate(got[i])
+        bound = 5e-5 + 1e-4 * np.abs(ref).max() if dtype == torch.float32 else 2.5e-2 * np.abs(ref).max()
+        # a token whose two best router logits nearly tie may go to the other expert in the engine;
+        # tokens after it then differ as well, so compare up to the first unsure token
+        upto = len(r) if sure.all() else int(np.argmin(sure))
+        assert upto >= 5
+        assert np.abs(g[:upto] - ref[:upto]).max() < bound, f"request {i}"
