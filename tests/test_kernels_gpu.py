@@ -36,7 +36,8 @@ def test_embed(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,eps", [(72, 1e-5), (4096, 1e-6), (1000, 3e-3)])
+@pytest.mark.parametrize("H,eps", [(72, 1e-5), (4096, 1e-6), (1000, 3e-3), (1001, 1e-5), (5120, 1e-5),
+                                   (18000, 1e-5)])
 def test_rmsnorm(dtype, H, eps):
     o = _ops(dtype)
     x = _rand((7, H), torch.float32, 2, 3.0)
@@ -180,10 +181,14 @@ def test_attention_generic(dtype, nh, nkv, hd, window):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
-def test_rope_cache_write(dtype, style):
+@pytest.mark.parametrize("nh,nkv,hd,lens,new", [(3, 2, 32, [66, 9], [66, 2]),
+                                                (5, 2, 128, [200, 131, 40], [200, 31, 40]),
+                                                (2, 1, 64, [300], [300]), (3, 3, 256, [260, 3], [260, 3]),
+                                                (3, 2, 32, [290, 9], [280, 2]), (4, 2, 48, [290], [290])])
+def test_rope_cache_write(dtype, style, nh, nkv, hd, lens, new):
+    """Few tokens and many (the many-token kernel turns the values in shared memory), runs of
+    positions that cross pages, and sequences that go on from an earlier step."""
     o = _ops(dtype)
-    nh, nkv, hd = 3, 2, 32
-    lens, new = [66, 9], [66, 2]
     pc = Paged(lens, nkv, hd, dtype, 30, poison=False)
     T = sum(new)
     qkv = _rand((T, (nh + 2 * nkv) * hd), torch.float32, 31)
@@ -290,7 +295,8 @@ def test_attention_decode_far_key_stands_out(use_tma):
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 4096, 4096), (16, 200, 72), (17, 384, 1000),
                                    (33, 130, 64), (64, 6144, 512), (100, 256, 176), (129, 128, 192),
-                                   (300, 520, 328), (2048, 512, 256)])
+                                   (300, 520, 328), (2048, 512, 256), (257, 700, 520),
+                                   (1000, 2500, 136), (2048, 4096, 512)])
 def test_gemm_tensor_core(M, N, K):
     from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16
     g = GemmBf16.get()

@@ -77,9 +77,74 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
   }
 }
 
+// Four values at a time: 16-byte loads of the row, 8- or 16-byte stores of the result.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 f = *reinterpret_cast<const float4*>(p);
+  v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&a);
+  u.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// The same norm for rows of H = 4n values that fit the block's registers (H <= 16 per thread).
+template <typename W>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                   const W* __restrict__ w, act_t* __restrict__ y, int H, float eps) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+  act_t* yr = y + (size_t)r * H;
+  float keep[4][4];
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = 4 * (threadIdx.x + j * blockDim.x);
+    if (i < H) load4(xr + i, keep[j]);
+    else keep[j][0] = keep[j][1] = keep[j][2] = keep[j][3] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ss = fmaf(keep[j][e], keep[j][e], ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = 4 * (threadIdx.x + j * blockDim.x);
+    if (i < H) {
+      float wv[4], o[4];
+      load4(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = (keep[j][e] / rms) * wv[e];
+      store4(yr + i, o);
+    }
+  }
+}
+
 extern "C" int TL_NAME(tl_rmsnorm)(const float* x, const int* rows, const void* w, int w_is_f32,
                                    void* y, int n_rows, int H, float eps, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (H % 4 == 0 && H <= 16384 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
+    const int vthreads = H <= 2048 ? 128 : H <= 4096 ? 256 : H <= 8192 ? 512 : 1024;
+    if (w_is_f32)
+      return tl_launch(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(vthreads), 0, stream, x, rows,
+                       (const float*)w, (act_t*)y, H, eps);
+    return tl_launch(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vthreads), 0, stream, x,
+                     rows, (const __nv_bfloat16*)w, (act_t*)y, H, eps);
+  }
   const int threads = H >= 2048 ? 512 : 256;
   if (w_is_f32)
     return tl_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, rows,
@@ -159,6 +224,87 @@ __global__ void rope_cache_write_kernel(const float* __restrict__ qkv, int ld,
   }
 }
 
+// The same for steps of many tokens, half-split pairs (style 0) and head sizes of 32, 64,
+// 128 or 256.  Two kinds of block in one launch:
+//  - blockIdx.y < rot_groups: one token; its query and key heads are rotated four pairs per
+//    lane with 16-byte loads, hd/8 lanes per head and 256/hd heads per warp at a time;
+//  - blockIdx.y == rot_groups: 32 consecutive tokens of one value head; the tile is turned
+//    in shared memory, so that the transposed value pages are written in runs of positions.
+__global__ void __launch_bounds__(128)
+rope_cache_write_vec_kernel(const float* __restrict__ qkv, int ld, act_t* __restrict__ q_out,
+                            act_t* __restrict__ k_pages, act_t* __restrict__ v_pages,
+                            const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                            const int* __restrict__ seq_slot, const int* __restrict__ page_table,
+                            int table_stride, const float* __restrict__ inv_freq, int T, int nh,
+                            int nkv, int hd, int rot_groups) {
+  extern __shared__ float vt[];   // [32 tokens][hd + 1]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if ((int)blockIdx.y == rot_groups) {
+    const int tiles_t = (T + 31) / 32;
+    for (int tile = blockIdx.x; tile < tiles_t * nkv; tile += gridDim.x) {
+      const int t0 = (tile / nkv) * 32, kvh = tile % nkv;
+      const int nt = min(32, T - t0);
+      const int vec_per_row = hd >> 2;
+      for (int idx = threadIdx.x; idx < nt * vec_per_row; idx += blockDim.x) {
+        const int tt = idx / vec_per_row, d = (idx % vec_per_row) * 4;
+        float v[4];
+        load4(qkv + (size_t)(t0 + tt) * ld + (size_t)(nh + nkv + kvh) * hd + d, v);
+        float* dst = vt + tt * (hd + 1) + d;
+        dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
+      }
+      __syncthreads();
+      if (lane < nt) {
+        const int t = t0 + lane;
+        const int pos = token_pos[t];
+        const int page = page_table[(size_t)seq_slot[token_seq[t]] * table_stride + pos / TL_PAGE];
+        act_t* dst = v_pages + ((size_t)page * nkv + kvh) * (size_t)(TL_PAGE * hd) + (pos % TL_PAGE);
+        for (int d = warp; d < hd; d += 4) dst[(size_t)d * TL_PAGE] = from_f32<act_t>(vt[lane * (hd + 1) + d]);
+      }
+      __syncthreads();
+    }
+    return;
+  }
+  const int t = blockIdx.x;
+  const int pos = token_pos[t];
+  const int half = hd >> 1;
+  const int lph = hd >> 3;            // lanes per head
+  const int hpp = 32 / lph;           // heads per warp pass
+  const int sub = lane / lph, i0 = (lane % lph) * 4;
+  const int page = page_table[(size_t)seq_slot[token_seq[t]] * table_stride + pos / TL_PAGE];
+  const float fpos = (float)pos;
+  float cs[4], sn[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    cs[j] = 1.0f; sn[j] = 0.0f;
+    if (inv_freq) sincosf(fpos * inv_freq[i0 + j], &sn[j], &cs[j]);
+  }
+  const int rot_heads = nh + nkv;
+  const int passes = (rot_heads + hpp - 1) / hpp;
+  const int per_group = (passes + rot_groups - 1) / rot_groups;
+  const int p_end = min(((int)blockIdx.y + 1) * per_group, passes);
+#pragma unroll 2
+  for (int p = (int)blockIdx.y * per_group + warp; p < p_end; p += 4) {
+    const int h = p * hpp + sub;
+    if (h >= rot_heads) continue;
+    const float* row = qkv + (size_t)t * ld + (size_t)h * hd;
+    act_t* dst = h < nh ? q_out + ((size_t)t * nh + h) * hd
+                        : k_pages + ((size_t)page * nkv + (h - nh)) * (size_t)(TL_PAGE * hd) +
+                              (size_t)(pos % TL_PAGE) * hd;
+    float a[4], b[4], lo[4], hi[4];
+    load4(row + i0, a);
+    load4(row + half + i0, b);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo[j] = a[j] * cs[j] - b[j] * sn[j];
+      hi[j] = a[j] * sn[j] + b[j] * cs[j];
+    }
+    store4(dst + i0, lo);
+    store4(dst + half + i0, hi);
+  }
+}
+
 extern "C" int TL_NAME(tl_rope_cache_write)(const float* qkv, int ld, void* q_out, void* k_pages,
                                             void* v_pages, const int* token_pos,
                                             const int* token_seq, const int* seq_slot,
@@ -168,6 +314,16 @@ extern "C" int TL_NAME(tl_rope_cache_write)(const float* qkv, int ld, void* q_ou
   if (T <= 0) return 0;
   if ((hd & 1) || hd > 256) return TL_ERR_BAD_ARG;
   const int heads = nh + (k_pages ? 2 * nkv : 0);
+  if (T >= 256 && style == 0 && k_pages && v_pages && (hd == 32 || hd == 64 || hd == 128 || hd == 256) &&
+      ld % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && nkv <= 65535) {
+    const int passes = (nh + nkv + 256 / hd - 1) / (256 / hd);
+    int rot_groups = (passes + 7) / 8;   // at most two passes for each of a block's four warps
+    if (rot_groups > 65534) return TL_ERR_UNSUPPORTED;
+    dim3 grid(T, rot_groups + 1);
+    return tl_launch(rope_cache_write_vec_kernel, grid, dim3(128), (size_t)32 * (hd + 1) * sizeof(float),
+                     stream, qkv, ld, (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages, token_pos,
+                     token_seq, seq_slot, page_table, table_stride, inv_freq, T, nh, nkv, hd, rot_groups);
+  }
   // few tokens: one warp per (token, head), for parallelism; many tokens: one block per token
   const int per_block = T >= 256 ? heads : 1;
   const int groups = (heads + per_block - 1) / per_block;

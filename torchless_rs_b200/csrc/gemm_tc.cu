@@ -621,6 +621,262 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w,
 }
 
 // ---------------------------------------------------------------------------
+// The persistent kernel on pairs of SMs (tcgen05 with cta_group::2).  The two blocks of a
+// cluster share one instruction of 256 weight rows x 256 tokens: each block holds 128 of
+// the weight rows and 128 of the tokens in its shared memory and 128 rows of the
+// accumulator in its tensor memory, so a block fetches 32 KB per 64 K-elements where the
+// one-SM kernel fetches 48 KB, and six stages fit instead of four.  The first block of
+// the pair issues the instructions; the barrier that says "stage filled" lives there and
+// counts the bytes of both blocks' TMA loads; the instruction's completion is signalled
+// to the "stage free" and "accumulator ready" barriers of both blocks at once.
+//
+// SiLU-gate mode: a block's 128 operand rows are 64 gate rows followed by the 64 up rows
+// of the same output columns, so one accumulator serves both; the epilogue threads of the
+// gate half and of the up half exchange half of their values through shared memory and
+// each write half of the tokens.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_saddr, uint32_t rank) {
+  uint32_t raddr;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_saddr), "r"(rank));
+  return raddr;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// TMA load whose bytes are counted by a barrier of either block of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(slot)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival at the barrier of the same place in both blocks of the pair, when all
+// instructions issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(smem_u32(bar)),
+      "h"((uint16_t)3)
+      : "memory");
+}
+// All 128 epilogue threads learn whether every one of them passed its wait.
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)ok)
+      : "memory");
+  return r != 0;
+}
+
+#define PAIR_BN 256       // tokens per pair tile
+#define PAIR_STAGE 32768  // bytes per stage and block: 128 operand rows + 128 token rows
+#define PAIR_XCHG 8192    // SiLU-gate exchange: two buffers of 2 x 8 x 64 floats
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
+                    const __grid_constant__ CUtensorMap tm_x, const GemmArgs args, int m_tiles,
+                    int total_tiles) {
+  constexpr uint32_t A_BYTES = 128 * TILE_K * 2;
+  constexpr uint32_t ACC_COLS = PAIR_BN;
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+  constexpr int PAIR_N = SWIGLU ? 128 : 256;   // output columns per pair tile
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PAIR_BN >> 3) << 17) |
+                             ((uint32_t)(256 >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stages = args.stages;
+  uint64_t* full_bar = (uint64_t*)(smem + (size_t)stages * PAIR_STAGE);
+  uint64_t* empty_bar = full_bar + 8;
+  uint64_t* acc_full = empty_bar + 8;    // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  float* xchg = (float*)(smem + (size_t)stages * PAIR_STAGE + 2048);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_total = (args.K + TILE_K - 1) / TILE_K;
+  const uint32_t rank = cluster_rank();          // 0 issues the instructions
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+  tc_fence_before();
+  cluster_sync_all();   // both blocks' barriers exist before either touches the other's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) pdl_launch_dependents();
+
+  if (warp == 4 && lane == 0) {
+    // ---- TMA producer of this block's halves; the bytes count at the first block's barrier
+    bool waited = false;
+    uint32_t it = 0;
+    for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+      const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * PAIR_BN;
+      for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) { tile = total_tiles; break; }
+        uint8_t* st = smem + (size_t)s * PAIR_STAGE;
+        if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * PAIR_STAGE);
+        const uint32_t bar = mapa_u32(smem_u32(&full_bar[s]), 0);
+        const int k = kb * TILE_K;
+        if (SWIGLU) {
+          tma_load_2d_pair(st, &tm_w, bar, k, n0 + 64 * (int)rank);
+          tma_load_2d_pair(st + A_BYTES / 2, &tm_w, bar, k, args.N + n0 + 64 * (int)rank);
+        } else {
+          tma_load_2d_pair(st, &tm_w, bar, k, n0 + 128 * (int)rank);
+        }
+        if (!waited) { pdl_wait(); waited = true; }
+        tma_load_2d_pair(st + A_BYTES, &tm_x, bar, k, m0 + 128 * (int)rank);
+      }
+    }
+  } else if (warp == 5 && lane == 0 && rank == 0) {
+    // ---- MMA issuer of the pair
+    uint32_t it = 0, local = 0;
+    bool ok = true;
+    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
+      const uint32_t buf = local & 1u;
+      ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1u) ^ 1u, abort_flag, 4);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + buf * ACC_COLS;
+      for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1u;
+        ok = mbar_wait(&full_bar[s], ph, abort_flag, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)s * PAIR_STAGE);
+        const uint64_t da = smem_desc_k128(sa);
+        const uint64_t db = smem_desc_k128(sa + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+          const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);
+          umma_bf16_pair(acc, da + adv, db + adv, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit_pair(&empty_bar[s]);
+      }
+      if (ok) umma_commit_pair(&acc_full[buf]);
+    }
+  } else if (warp < 4) {
+    // ---- epilogue of this block's 128 accumulator rows
+    pdl_wait();
+    const int row = warp * 32 + lane;
+    const uint32_t acc_empty_leader = mapa_u32(smem_u32(&acc_empty[0]), 0);
+    uint32_t local = 0;
+    for (int tile = pair; tile < total_tiles; tile += n_pairs, ++local) {
+      const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * PAIR_BN;
+      const uint32_t buf = local & 1u;
+      if (!epilogue_all(mbar_wait(&acc_full[buf], (local >> 1) & 1u, abort_flag, 3))) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * ACC_COLS;
+      if (SWIGLU) {
+        // rows 0-63 hold the gate, rows 64-127 the up value of column n; the gate half
+        // writes tokens 0-7 of each 16, the up half tokens 8-15
+        const int col = row & 63, up_half = row >> 6;
+        const int n = n0 + 64 * (int)rank + col;
+        for (int c0 = 0, i = 0; c0 < PAIR_BN; c0 += 16, ++i) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+          float* mine = xchg + (i & 1) * 1024 + (up_half ? 512 : 0);     // what I give away
+          float* theirs = xchg + (i & 1) * 1024 + (up_half ? 0 : 512);   // what I get
+#pragma unroll
+          for (int j = 0; j < 8; ++j) mine[j * 64 + col] = __uint_as_float(r[up_half ? j : 8 + j]);
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (n < args.N) {
+            const int t0 = m0 + c0 + (up_half ? 8 : 0);
+            __nv_bfloat16* cb = (__nv_bfloat16*)args.C + (size_t)t0 * args.ldc + n;
+            const int valid = args.M - t0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (j >= valid) break;
+              const float other = theirs[j * 64 + col];
+              const float g = up_half ? other : __uint_as_float(r[j]);
+              const float u = up_half ? __uint_as_float(r[8 + j]) : other;
+              cb[(size_t)j * args.ldc] = __float2bfloat16_rn(silu_f(g) * u);
+            }
+          }
+        }
+      } else {
+        const int n = n0 + 128 * (int)rank + row;
+        for (int c0 = 0; c0 < PAIR_BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+          if (n < args.N) {
+            float* cf = (float*)args.C + (size_t)(m0 + c0) * args.ldc + n;
+            __nv_bfloat16* cb = (__nv_bfloat16*)args.C + (size_t)(m0 + c0) * args.ldc + n;
+            const int valid = args.M - (m0 + c0);
+            if (args.mode == MODE_ACCUM_F32) {
+              float prev[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) prev[j] = j < valid ? cf[(size_t)j * args.ldc] : 0.0f;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (j < valid) cf[(size_t)j * args.ldc] = prev[j] + __uint_as_float(r[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (j >= valid) break;
+                const float v = __uint_as_float(r[j]);
+                if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
+                else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(acc_empty_leader + 8 * buf);   // 256 arrivals free the accumulator
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  cluster_sync_all();   // neither block leaves, nor frees tensor memory, while the other works
+  if (warp == 0) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
 // Host side: tensor maps (cached), tile and split choice, launch.
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -736,6 +992,46 @@ static int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, GemmA
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
+// The pair kernel: clusters of two blocks, as many as the GPU holds at once.
+template <bool SWIGLU>
+static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, cudaStream_t stream) {
+  const int stages = 6;
+  a.stages = stages;
+  const size_t smem = 1024 + (size_t)stages * PAIR_STAGE + 2048 + PAIR_XCHG;
+  const int m_tiles = (a.M + PAIR_BN - 1) / PAIR_BN;
+  const int pair_n = SWIGLU ? 128 : 256;
+  const int total = m_tiles * ((a.N + pair_n - 1) / pair_n);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  static const int pdl_on = getenv("TL_NO_PDL") ? 0 : 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_on;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  static int max_pairs = -1;   // per instantiation
+  if (max_pairs < 0) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<SWIGLU>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    cfg.gridDim = dim3(2);
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<SWIGLU>, &cfg);
+    if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
+    max_pairs = n;
+  }
+  if (max_pairs <= 0) return -2;
+  cfg.gridDim = dim3(2 * (total < max_pairs ? total : max_pairs));
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU>, tw, tx, a, m_tiles, total);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
 #define MAX_SPLITS 8   // portable cluster size
 
 // What the caller passes to have rotation and cache write done by the q/k/v product.
@@ -796,6 +1092,17 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   // the SiLU-gate's two accumulators per tile)
   const bool persistent = M > 128 && !ss_in;
   if (persistent) bn = swiglu ? 128 : 256;
+  static const int pair_on = getenv("TL_NO_PAIR") ? 0 : 1;
+  if (persistent && pair_on) {
+    CUtensorMap pw, px;
+    if (make_map(&pw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, swiglu ? 64 : 128) &&
+        make_map(&px, X, M, K, ldx, 128)) {
+      GemmArgs p = {};
+      p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.mode = mode;
+      const int rc = swiglu ? launch_pair<true>(pw, px, p, stream) : launch_pair<false>(pw, px, p, stream);
+      if (rc != -2) return rc;
+    }
+  }
   CUtensorMap tw, tx;
   if (!make_map(&tw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, TILE_N)) return -2;
   if (!make_map(&tx, X, M, K, ldx, bn)) return -2;
