@@ -296,7 +296,10 @@ def test_attention_decode_far_key_stands_out(use_tma):
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 4096, 4096), (16, 200, 72), (17, 384, 1000),
                                    (33, 130, 64), (64, 6144, 512), (100, 256, 176), (129, 128, 192),
                                    (300, 520, 328), (2048, 512, 256), (257, 700, 520),
-                                   (1000, 2500, 136), (2048, 4096, 512)])
+                                   (1000, 2500, 136), (2048, 4096, 512), (1024, 5000, 2048),
+                                   (100, 512, 4096), (200, 384, 2048), (300, 640, 4096),
+                                   (300, 4096, 1024), (130, 6100, 768), (70, 4096, 4096),
+                                   (300, 256, 14336), (200, 384, 8192)])
 def test_gemm_tensor_core(M, N, K):
     from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16
     g = GemmBf16.get()

@@ -121,6 +121,19 @@ def _run_with_progress(cmd: List[str], what: str) -> None:
         raise BuildError(f"nvcc failed for {what}:\n{' '.join(cmd)}\n{''.join(out)}")
 
 
+def _remove_stale(name: str, keep: str) -> None:
+    """Builds of the same library from older sources (another digest in the name) go away."""
+    prefix, bdir = f"libtl_{name}_", os.path.dirname(keep)
+    for f in os.listdir(bdir):
+        rest = f[len(prefix):-3] if f.startswith(prefix) and f.endswith(".so") else ""
+        if len(rest) == 12 and all(c in "0123456789abcdef" for c in rest) and \
+                os.path.join(bdir, f) != keep:
+            try:
+                os.remove(os.path.join(bdir, f))
+            except OSError:
+                pass
+
+
 def build_library(name: str, verbose: bool = True, extra_flags: Sequence[str] = ()) -> str:
     """Compiles the library if its file is not there yet; returns the path."""
     if name not in LIBRARIES:
@@ -149,6 +162,7 @@ def build_library(name: str, verbose: bool = True, extra_flags: Sequence[str] = 
         _run_with_progress([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs, "-lcudart"],
                            f"link {name}")
         os.replace(tmp, path)  # atomic: a concurrent builder ends with the same file
+        _remove_stale(name, path)
     finally:
         for o in objs:
             if os.path.exists(o):

@@ -703,12 +703,20 @@ __device__ __forceinline__ bool epilogue_all(bool ok) {
 #define PAIR_BN 256       // tokens per pair tile
 #define PAIR_STAGE 32768  // bytes per stage and block: 128 operand rows + 128 token rows
 #define PAIR_XCHG 8192    // SiLU-gate exchange: two buffers of 2 x 8 x 64 floats
+#define PAIR_MAX_BLOCKS 160
+
+// A product with fewer tiles than pairs splits K over `splits` pairs per tile, all running
+// at once.  The pair with the first K-blocks writes C; the others leave their partial tiles
+// here, one slot per block, and raise the block's flag; the writer adds them in split order
+// (the same bits every run) and lowers the flags again.
+__device__ float tl_pair_partial[PAIR_MAX_BLOCKS * 128 * PAIR_BN];
+__device__ unsigned int tl_pair_flag[PAIR_MAX_BLOCKS];
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_x, const GemmArgs args, int m_tiles,
-                    int total_tiles) {
+                    int total_tiles, int splits) {
   constexpr uint32_t A_BYTES = 128 * TILE_K * 2;
   constexpr uint32_t ACC_COLS = PAIR_BN;
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
@@ -731,6 +739,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
   const int kb_total = (args.K + TILE_K - 1) / TILE_K;
   const uint32_t rank = cluster_rank();          // 0 issues the instructions
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  // work item = (tile, split); with splits > 1 the grid holds every item at once
+  const int total_items = total_tiles * splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -749,12 +759,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     // ---- TMA producer of this block's halves; the bytes count at the first block's barrier
     bool waited = false;
     uint32_t it = 0;
-    for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+    for (int item = pair; item < total_items; item += n_pairs) {
+      const int tile = item / splits, split = item % splits;
       const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * PAIR_BN;
-      for (int kb = 0; kb < kb_total; ++kb, ++it) {
+      const int kb_b = split * args.kb_per_split, kb_e = min(kb_total, kb_b + args.kb_per_split);
+      for (int kb = kb_b; kb < kb_e; ++kb, ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1u;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) { tile = total_tiles; break; }
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) { item = total_items; break; }
         uint8_t* st = smem + (size_t)s * PAIR_STAGE;
         if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * PAIR_STAGE);
         const uint32_t bar = mapa_u32(smem_u32(&full_bar[s]), 0);
@@ -773,13 +785,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     // ---- MMA issuer of the pair
     uint32_t it = 0, local = 0;
     bool ok = true;
-    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
+    for (int item = pair; item < total_items && ok; item += n_pairs, ++local) {
+      const int split = item % splits;
+      const int kb_b = split * args.kb_per_split, kb_e = min(kb_total, kb_b + args.kb_per_split);
       const uint32_t buf = local & 1u;
       ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1u) ^ 1u, abort_flag, 4);
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + buf * ACC_COLS;
-      for (int kb = 0; kb < kb_total; ++kb, ++it) {
+      for (int kb = kb_b; kb < kb_e; ++kb, ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1u;
         ok = mbar_wait(&full_bar[s], ph, abort_flag, 2);
@@ -791,7 +805,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
 #pragma unroll
         for (int k = 0; k < TILE_K / UMMA_K; ++k) {
           const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);
-          umma_bf16_pair(acc, da + adv, db + adv, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_bf16_pair(acc, da + adv, db + adv, IDESC, (kb > kb_b || k > 0) ? 1u : 0u);
         }
         umma_commit_pair(&empty_bar[s]);
       }
@@ -802,14 +816,42 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     pdl_wait();
     const int row = warp * 32 + lane;
     const uint32_t acc_empty_leader = mapa_u32(smem_u32(&acc_empty[0]), 0);
+    float* my_partial = tl_pair_partial + (size_t)blockIdx.x * (128 * PAIR_BN) + row;
     uint32_t local = 0;
-    for (int tile = pair; tile < total_tiles; tile += n_pairs, ++local) {
+    for (int item = pair; item < total_items; item += n_pairs, ++local) {
+      const int tile = item / splits, split = item % splits;
       const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * PAIR_BN;
       const uint32_t buf = local & 1u;
-      if (!epilogue_all(mbar_wait(&acc_full[buf], (local >> 1) & 1u, abort_flag, 3))) break;
+      const bool merge = splits > 1 && split == 0;   // this pair writes C
+      bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1u, abort_flag, 3);
+      if (merge && ok && threadIdx.x < (unsigned)(splits - 1)) {
+        // thread j waits for the partial tile of split j + 1 (same rank, two blocks further each)
+        ok = false;
+        for (uint32_t i = 0; i < WAIT_LIMIT && !ok; ++i) {
+          unsigned int f;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
+                       : "=r"(f) : "l"(&tl_pair_flag[blockIdx.x + 2 * (threadIdx.x + 1)]) : "memory");
+          ok = f != 0;
+          if (!ok) __nanosleep(64);
+        }
+        if (!ok) { *abort_flag = 5; atomicCAS(&tl_gemm_tc_error, 0, 5); }
+      }
+      if (!epilogue_all(ok)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * ACC_COLS;
-      if (SWIGLU) {
+      if (split > 0) {
+        for (int c0 = 0; c0 < PAIR_BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) my_partial[(c0 + j) * 128] = __uint_as_float(r[j]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 0)
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(&tl_pair_flag[blockIdx.x]), "r"(1u) : "memory");
+      } else if (SWIGLU) {
         // rows 0-63 hold the gate, rows 64-127 the up value of column n; the gate half
         // writes tokens 0-7 of each 16, the up half tokens 8-15
         const int col = row & 63, up_half = row >> 6;
@@ -818,6 +860,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
           uint32_t r[16];
           tmem_ld16(taddr + c0, r);
           tmem_ld_wait();
+          if (merge) {
+            for (int sp = 1; sp < splits; ++sp) {
+              const float* part = my_partial + (size_t)(2 * sp) * (128 * PAIR_BN) + c0 * 128;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(part + j * 128));
+            }
+          }
           float* mine = xchg + (i & 1) * 1024 + (up_half ? 512 : 0);     // what I give away
           float* theirs = xchg + (i & 1) * 1024 + (up_half ? 0 : 512);   // what I get
 #pragma unroll
@@ -837,34 +886,70 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
             }
           }
         }
+      } else if (args.mode == MODE_ACCUM_F32) {
+        // 64 values of C are fetched at once: four round trips to memory per tile, which
+        // matters for the last tile, whose epilogue nothing hides
+        const int n = n0 + 128 * (int)rank + row;
+        for (int c0 = 0; c0 < PAIR_BN; c0 += 64) {
+          float prev[64];
+          float* cf = (float*)args.C + (size_t)(m0 + c0) * args.ldc + n;
+          const int valid = args.M - (m0 + c0);
+#pragma unroll
+          for (int j = 0; j < 64; ++j) prev[j] = (n < args.N && j < valid) ? cf[(size_t)j * args.ldc] : 0.0f;
+          float part[64];   // the other splits' sums, added in split order, then to the accumulator
+#pragma unroll
+          for (int j = 0; j < 64; ++j) part[j] = 0.0f;
+          if (merge) {
+            for (int sp = 1; sp < splits; ++sp) {
+              const float* src = my_partial + (size_t)(2 * sp) * (128 * PAIR_BN) + c0 * 128;
+#pragma unroll
+              for (int j = 0; j < 64; ++j) part[j] += __ldcg(src + j * 128);
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t r[16];
+            tmem_ld16(taddr + c0 + 16 * q, r);
+            tmem_ld_wait();
+            if (n < args.N) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (16 * q + j < valid)
+                  cf[(size_t)(16 * q + j) * args.ldc] = prev[16 * q + j] + (__uint_as_float(r[j]) + part[16 * q + j]);
+            }
+          }
+        }
       } else {
         const int n = n0 + 128 * (int)rank + row;
         for (int c0 = 0; c0 < PAIR_BN; c0 += 16) {
           uint32_t r[16];
           tmem_ld16(taddr + c0, r);
           tmem_ld_wait();
+          if (merge) {
+            for (int sp = 1; sp < splits; ++sp) {
+              const float* part = my_partial + (size_t)(2 * sp) * (128 * PAIR_BN) + c0 * 128;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(part + j * 128));
+            }
+          }
           if (n < args.N) {
             float* cf = (float*)args.C + (size_t)(m0 + c0) * args.ldc + n;
             __nv_bfloat16* cb = (__nv_bfloat16*)args.C + (size_t)(m0 + c0) * args.ldc + n;
             const int valid = args.M - (m0 + c0);
-            if (args.mode == MODE_ACCUM_F32) {
-              float prev[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) prev[j] = j < valid ? cf[(size_t)j * args.ldc] : 0.0f;
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (j < valid) cf[(size_t)j * args.ldc] = prev[j] + __uint_as_float(r[j]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (j >= valid) break;
-                const float v = __uint_as_float(r[j]);
-                if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
-                else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
-              }
+            for (int j = 0; j < 16; ++j) {
+              if (j >= valid) break;
+              const float v = __uint_as_float(r[j]);
+              if (args.mode == MODE_STORE_F32) cf[(size_t)j * args.ldc] = v;
+              else cb[(size_t)j * args.ldc] = __float2bfloat16_rn(v);
             }
           }
         }
+      }
+      if (merge) {   // every thread has read the partial tiles: their flags go back to 0
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x < (unsigned)(splits - 1))
+          asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(&tl_pair_flag[blockIdx.x + 2 * (threadIdx.x + 1)]), "r"(0u) : "memory");
       }
       tc_fence_before();
       mbar_arrive_cluster(acc_empty_leader + 8 * buf);   // 256 arrivals free the accumulator
@@ -994,7 +1079,8 @@ static int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, GemmA
 
 // The pair kernel: clusters of two blocks, as many as the GPU holds at once.
 template <bool SWIGLU>
-static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, cudaStream_t stream) {
+static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int want_splits,
+                       cudaStream_t stream) {
   const int stages = 6;
   a.stages = stages;
   const size_t smem = 1024 + (size_t)stages * PAIR_STAGE + 2048 + PAIR_XCHG;
@@ -1024,11 +1110,18 @@ static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a,
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<SWIGLU>, &cfg);
     if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
-    max_pairs = n;
+    max_pairs = n < PAIR_MAX_BLOCKS / 2 ? n : PAIR_MAX_BLOCKS / 2;
   }
   if (max_pairs <= 0) return -2;
-  cfg.gridDim = dim3(2 * (total < max_pairs ? total : max_pairs));
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU>, tw, tx, a, m_tiles, total);
+  // K split over several pairs per tile only while every (tile, split) runs at once
+  const int kb_total = (a.K + TILE_K - 1) / TILE_K;
+  int splits = want_splits;
+  while (splits > 1 && (long long)total * splits > max_pairs) --splits;
+  a.kb_per_split = (kb_total + splits - 1) / splits;
+  splits = (kb_total + a.kb_per_split - 1) / a.kb_per_split;   // no empty split
+  const int items = total * splits;
+  cfg.gridDim = dim3(2 * (items < max_pairs ? items : max_pairs));
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU>, tw, tx, a, m_tiles, total, splits);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -1079,27 +1172,44 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   const size_t budget = !two_per_sm ? 224 * 1024 : (!swiglu && bn <= 32) ? 80 * 1024 : 112 * 1024;
   const long long slots = (long long)num_sms * (two_per_sm ? 2 : 1);
   int splits = 1;
-  if (tiles < slots && two_per_sm) {
+  if (tiles < slots && (two_per_sm || !ss_in)) {
     // a power of two (clusters of 3, 5, 6 or 7 blocks do not tile the GPCs evenly, and a
     // cluster that has to wait for a second wave doubles the kernel's time), as large as
     // keeps every block resident at once
     while (splits * 2 <= MAX_SPLITS && tiles * splits * 2 <= slots && splits * 2 <= kb_total / 2)
       splits *= 2;
+    // token tiles of 128: the reduction of so wide a tile costs about 40 K-blocks' time
+    // (measured), so the split has to save more than that
+    if (!two_per_sm && (kb_total + splits - 1) / splits + 40 >= kb_total) splits = 1;
   }
   int kb_per_split = (kb_total + splits - 1) / splits;
   splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
-  // many tokens: the persistent kernel with two accumulators (token tile 256, or 128 with
-  // the SiLU-gate's two accumulators per tile)
+  // Many tokens: the persistent kernels with two accumulators.
   const bool persistent = M > 128 && !ss_in;
   if (persistent) bn = swiglu ? 128 : 256;
   static const int pair_on = getenv("TL_NO_PAIR") ? 0 : 1;
-  if (persistent && pair_on) {
+  const int pairs = num_sms / 2;
+  const int pair_n = swiglu ? 128 : 256;
+  const long long tiles_p = (long long)((N + pair_n - 1) / pair_n) * ((M + PAIR_BN - 1) / PAIR_BN);
+  // K split over idle pairs: the merge of s partial tiles costs about 16 + 24 (s - 1)
+  // K-blocks' time (measured)
+  int pair_splits = 1;
+  if (pairs > 0 && tiles_p * 2 <= pairs) {
+    long long best = kb_total;
+    for (int sp = 2; sp <= 8 && tiles_p * sp <= pairs && sp <= kb_total / 4; ++sp) {
+      const long long cost = (kb_total + sp - 1) / sp + 16 + 24 * (sp - 1);
+      if (cost < best) { best = cost; pair_splits = sp; }
+    }
+  }
+  const bool use_pair = persistent;
+  if (use_pair && pair_on) {
     CUtensorMap pw, px;
     if (make_map(&pw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, swiglu ? 64 : 128) &&
         make_map(&px, X, M, K, ldx, 128)) {
       GemmArgs p = {};
       p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.mode = mode;
-      const int rc = swiglu ? launch_pair<true>(pw, px, p, stream) : launch_pair<false>(pw, px, p, stream);
+      const int rc = swiglu ? launch_pair<true>(pw, px, p, pair_splits, stream)
+                            : launch_pair<false>(pw, px, p, pair_splits, stream);
       if (rc != -2) return rc;
     }
   }
@@ -1147,10 +1257,15 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
 }
 
 // Reads and clears the error word that a kernel sets when one of its bounded waits ran
-// out (0 = none; 1 producer, 2 issuer, 3 epilogue).  Synchronises the device.
+// out (0 = none; 1 producer, 2 issuer, 3 epilogue, 4 accumulator, 5 another pair's partial
+// tile).  Synchronises the device.
 extern "C" int tl_gemm_tc_take_error() {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, tl_gemm_tc_error, sizeof(int)) != cudaSuccess) return -1;
-  if (v) cudaMemcpyToSymbol(tl_gemm_tc_error, &zero, sizeof(int));
+  if (v) {
+    cudaMemcpyToSymbol(tl_gemm_tc_error, &zero, sizeof(int));
+    static const unsigned int zeros[PAIR_MAX_BLOCKS] = {};
+    cudaMemcpyToSymbol(tl_pair_flag, zeros, sizeof(zeros));   // a kernel that gave up may leave flags up
+  }
   return v;
 }
