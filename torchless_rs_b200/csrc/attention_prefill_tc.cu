@@ -10,8 +10,14 @@
 //               when some row's maximum moved
 //   O[128, hd] += P . V          tcgen05.mma, P from shared memory, the page's transposed V
 //                                slab as the K-major B operand
-// Pages come by TMA (three in flight).  Arithmetic as in attention_prefill_bf16.cu
-// (reference: src/model/modules/attention.rs:88-121, src/model/modules/flash_attention.rs:
+// S has two buffers in tensor memory: Q . K^T of page i + 1 is issued (by a thread of its
+// own) before the softmax of page i has ended, and P . V of page i (issued by another thread)
+// runs under the softmax of page i + 1, so the softmax warps rarely wait for a product.  Pages
+// come by TMA, K slabs one page ahead of V slabs.  What was measured with clock64() stamps in
+// one block: per page the softmax takes about 1100 cycles of arithmetic (bound by the
+// 16 exponentials a cycle of an SM when two blocks share it), 450 for the P stores and the
+// proxy fence, 200 for the barrier; issuing one tcgen05.mma costs its thread about 80 cycles.
+// Arithmetic as in attention_prefill_bf16.cu (reference: src/model/modules/attention.rs:88-121, src/model/modules/flash_attention.rs:
 // 101-136, window of src/model/models/gpt_oss.rs:168-176).  Head sizes 64 and 128.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the block records a code in
@@ -26,8 +32,12 @@
 #include <tuple>
 
 #define TC_Q 128                         // queries per block
-#define TC_STAGES 2                      // two blocks per SM: one block's products overlap the other's softmax
-#define TC_THREADS 192                   // warps 0-3 softmax, warp 4 TMA, warp 5 MMA
+// Two blocks per SM (one block's products overlap the other's softmax) leave each block room
+// for five page slabs beside its queries: three of K, whose page i + 1 is wanted one softmax
+// earlier than its V, and two of V.  K(i + 1) and V(i) take the slabs that P(i-2) . V(i-2) frees.
+#define TC_KSLOTS 3
+#define TC_VSLOTS 2
+#define TC_THREADS 224                   // warps 0-3 softmax, warp 4 TMA, warp 5 issues Q.K^T, warp 6 issues P.V
 #define TC_KSUB (HEAD_DIM / 64)
 #define TC_Q_BYTES (TC_Q * HEAD_DIM * 2)
 #define TC_K_BYTES (PAGE * HEAD_DIM * 2)
@@ -36,11 +46,12 @@
 // written over that slab, which Q.K^T has finished with, and needs no buffer of its own
 #define TC_P_IN_K (HEAD_DIM == 128)
 #define TC_P_BYTES (TC_P_IN_K ? 0 : TC_Q * PAGE * 2)
-#define TC_STAGE_BYTES (TC_K_BYTES + TC_V_BYTES)
+#define TC_SMEM_BYTES (TC_Q_BYTES + TC_P_BYTES + TC_KSLOTS * TC_K_BYTES + TC_VSLOTS * TC_V_BYTES + 256)
 #define TC_WAIT_LIMIT (1u << 22)
-#define TC_TMEM_COLS (HEAD_DIM == 128 ? 256 : 128)   // S (64 columns) then O (HEAD_DIM columns)
+#define TC_TMEM_COLS 256   // S twice (64 columns each), then O (HEAD_DIM columns)
 
 __device__ int tl_attn_tc_error = 0;
+
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tc_mbar_init(uint64_t* bar, uint32_t count) {
@@ -86,6 +97,25 @@ __device__ __forceinline__ void tc_umma(uint32_t tmem_d, uint64_t da, uint64_t d
       : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
       : "memory");
 }
+// A wait that lets the hardware park the thread (up to about a microsecond per try) instead of
+// spinning: the spinning threads would take issue slots from the softmax warps.
+__device__ __forceinline__ bool tc_mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  for (uint32_t i = 0; i < (TC_WAIT_LIMIT >> 2); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(tc_smem_u32(bar)), "r"(parity), "r"(1000u)
+        : "memory");
+    if (ok) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = code;
+  atomicCAS(&tl_attn_tc_error, 0, code);
+  return false;
+}
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem_u32(bar))
                : "memory");
@@ -116,6 +146,36 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ float tc_ex2(float x) {   // 2^x, one instruction; tiny results flush to zero
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Two 32-bit floats in one 64-bit register, and the packed arithmetic of sm_100 on them.
+__device__ __forceinline__ uint64_t tc_pack2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void tc_unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t tc_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t tc_add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float tc_max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+
 // K-major tile with 128-byte rows and the 128-byte swizzle: 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t tc_desc(uint32_t saddr) {
   uint64_t d = 0;
@@ -136,19 +196,26 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
                            const int* __restrict__ seq_start, const int* __restrict__ seq_len,
                            const int* __restrict__ seq_slot, const int* __restrict__ page_table,
                            int table_stride, int nh, int nkv, int window, float scale_log2) {
-  extern __shared__ uint8_t tc_smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+  // The tiles need 1024-byte alignment (128-byte swizzle) and two blocks per SM leave no room
+  // for padding, so the dynamic shared memory itself must start on such a boundary (it does
+  // when the kernel has no static shared memory; checked below).
+  extern __shared__ __align__(1024) uint8_t tc_smem_raw[];
+  uint8_t* smem = tc_smem_raw;
   uint8_t* q_s = smem;
   uint8_t* p_s = q_s + TC_Q_BYTES;
-  uint8_t* kv_s = p_s + TC_P_BYTES;
-  uint64_t* q_full = (uint64_t*)(kv_s + TC_STAGES * TC_STAGE_BYTES);
-  uint64_t* kv_full = q_full + 1;
-  uint64_t* kv_empty = kv_full + TC_STAGES;
-  uint64_t* s_full = kv_empty + TC_STAGES;
-  uint64_t* p_full = s_full + 1;
-  uint64_t* o_done = p_full + 1;
+  uint8_t* k_s = p_s + TC_P_BYTES;
+  uint8_t* v_s = k_s + TC_KSLOTS * TC_K_BYTES;
+  uint64_t* q_full = (uint64_t*)(v_s + TC_VSLOTS * TC_V_BYTES);
+  uint64_t* k_full = q_full + 1;
+  uint64_t* k_empty = k_full + TC_KSLOTS;
+  uint64_t* v_full = k_empty + TC_KSLOTS;
+  uint64_t* v_empty = v_full + TC_VSLOTS;
+  uint64_t* s_full = v_empty + TC_VSLOTS;   // [2], one per S buffer
+  uint64_t* p_full = s_full + 2;             // [2]
+  uint64_t* o_done = p_full + 2;
   uint32_t* tmem_slot = (uint32_t*)(o_done + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  volatile int* pv_issued = abort_flag + 1;   // pages whose P . V the second issuer has issued
 
   const int b = blockIdx.z, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -159,14 +226,19 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
   // the last queries of a sequence see the most keys: their blocks come first in the grid
   const int blk0 = (int)(gridDim.x - 1 - blockIdx.x) * TC_Q;
   if (blk0 >= n_new) return;   // before any tensor memory is taken
+  if (tc_smem_u32(tc_smem_raw) & 1023u) {   // see above; nothing has been allocated yet
+    if (threadIdx.x == 0) atomicCAS(&tl_attn_tc_error, 0, 9);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     tc_mbar_init(q_full, 1);
-    for (int s = 0; s < TC_STAGES; ++s) { tc_mbar_init(&kv_full[s], 1); tc_mbar_init(&kv_empty[s], 1); }
-    tc_mbar_init(s_full, 1);
-    tc_mbar_init(p_full, 128);
+    for (int s = 0; s < TC_KSLOTS; ++s) { tc_mbar_init(&k_full[s], 1); tc_mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < TC_VSLOTS; ++s) { tc_mbar_init(&v_full[s], 1); tc_mbar_init(&v_empty[s], 1); }
+    for (int u = 0; u < 2; ++u) { tc_mbar_init(&s_full[u], 1); tc_mbar_init(&p_full[u], 128); }
     tc_mbar_init(o_done, 1);
     *abort_flag = 0;
+    *pv_issued = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -179,7 +251,7 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + PAGE;   // S takes the first 64 columns
+  const uint32_t tmem_o = tmem_base + 2 * PAGE;   // the two S buffers take the first 128 columns
 
   const int len = seq_len[b];
   const int past = len - n_new;
@@ -197,57 +269,79 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
 #pragma unroll
     for (int sub = 0; sub < TC_KSUB; ++sub)
       tc_tma_load_2d(q_s + sub * (TC_Q * 128), &tm_q, q_full, h * HEAD_DIM + sub * 64, tok0 + blk0);
-    for (int i = 0; i < n_pg; ++i) {
-      const int s = i % TC_STAGES;
-      if (!tc_mbar_wait(&kv_empty[s], ((uint32_t)(i / TC_STAGES) & 1u) ^ 1u, abort_flag, 1)) break;
-      const int slab = table[ps + i] * nkv + kvh;
-      uint8_t* st = kv_s + (size_t)s * TC_STAGE_BYTES;
-      tc_mbar_expect_tx(&kv_full[s], TC_STAGE_BYTES);
+    for (int i = 0; i <= n_pg; ++i) {
+      if (i < n_pg) {
+        const int s = i % TC_KSLOTS;
+        if (!tc_mbar_wait_parked(&k_empty[s], ((uint32_t)(i / TC_KSLOTS) & 1u) ^ 1u, abort_flag, 1)) break;
+        const int slab = table[ps + i] * nkv + kvh;
+        tc_mbar_expect_tx(&k_full[s], TC_K_BYTES);
 #pragma unroll
-      for (int sub = 0; sub < TC_KSUB; ++sub)
-        tc_tma_load_2d(st + sub * (PAGE * 128), &tm_k, &kv_full[s], sub * 64, slab * PAGE);
-      tc_tma_load_2d(st + TC_K_BYTES, &tm_v, &kv_full[s], 0, slab * HEAD_DIM);
-    }
-  } else if (warp == 5 && lane == 0) {
-    // ---- MMA issuer
-    const uint32_t idesc_s = tc_idesc(PAGE), idesc_o = tc_idesc(HEAD_DIM);
-    const uint32_t qa = tc_smem_u32(q_s);
-    bool ok = tc_mbar_wait(q_full, 0, abort_flag, 2);
-    auto issue_pv = [&](int j) {   // O (+)= P(j) . V(j)
-      const uint32_t st_j = tc_smem_u32(kv_s + (size_t)(j % TC_STAGES) * TC_STAGE_BYTES);
-      const uint32_t va = st_j + TC_K_BYTES;
-      const uint32_t pa = TC_P_IN_K ? st_j : tc_smem_u32(p_s);
-#pragma unroll
-      for (int k = 0; k < PAGE / 16; ++k)
-        tc_umma(tmem_o, tc_desc(pa) + (uint64_t)(k * 2), tc_desc(va) + (uint64_t)(k * 2), idesc_o,
-                (j > 0 || k > 0) ? 1u : 0u);
-      tc_commit(&kv_empty[j % TC_STAGES]);   // the page's stage is free once these have read it
-      tc_commit(o_done);
-    };
-    for (int i = 0; i < n_pg && ok; ++i) {
-      const int s = i % TC_STAGES;
-      ok = tc_mbar_wait(&kv_full[s], (uint32_t)(i / TC_STAGES) & 1u, abort_flag, 3);
-      if (!ok) break;
+        for (int sub = 0; sub < TC_KSUB; ++sub)
+          tc_tma_load_2d(k_s + (size_t)s * TC_K_BYTES + sub * (PAGE * 128), &tm_k, &k_full[s], sub * 64, slab * PAGE);
+      }
       if (i > 0) {
-        ok = tc_mbar_wait(p_full, (uint32_t)(i - 1) & 1u, abort_flag, 4);
+        const int j = i - 1, s = j % TC_VSLOTS;
+        if (!tc_mbar_wait_parked(&v_empty[s], ((uint32_t)(j / TC_VSLOTS) & 1u) ^ 1u, abort_flag, 1)) break;
+        const int slab = table[ps + j] * nkv + kvh;
+        tc_mbar_expect_tx(&v_full[s], TC_V_BYTES);
+        tc_tma_load_2d(v_s + (size_t)s * TC_V_BYTES, &tm_v, &v_full[s], 0, slab * HEAD_DIM);
+      }
+    }
+  } else if ((warp == 5 || warp == 6) && lane == 0) {
+    // ---- two MMA issuers.  Issuing costs some 80 cycles an instruction, twelve instructions a
+    // page, so one thread (warp 5) issues Q . K^T and another (warp 6) P . V.  A descriptor is a
+    // constant high word and a low word = (address >> 4) | 1 << 16.
+    const uint32_t idesc_s = tc_idesc(PAGE), idesc_o = tc_idesc(HEAD_DIM);
+    const uint32_t desc_hi = (uint32_t)(tc_desc(0) >> 32);
+    auto lo_of = [](uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); };
+    auto desc_of = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
+    const uint32_t q_lo = lo_of(tc_smem_u32(q_s));
+    const uint32_t k_lo = lo_of(tc_smem_u32(k_s)), v_lo = lo_of(tc_smem_u32(v_s));
+    const uint32_t p_lo = TC_P_IN_K ? k_lo : lo_of(tc_smem_u32(p_s));
+    bool ok = true;
+    if (warp == 5) {
+      // S(j) = Q . K(j)^T into buffer j & 1, up to two pages ahead of the softmax
+      ok = tc_mbar_wait_parked(q_full, 0, abort_flag, 2);
+      for (int j = 0; j < n_pg && ok; ++j) {
+        if (j >= 2) {
+          // the buffer is free when the softmax of page j - 2 has read it; and the other issuer
+          // must have seen that same phase of the barrier before the next one can complete
+          ok = tc_mbar_wait_parked(&p_full[j & 1], (uint32_t)((j - 2) >> 1) & 1u, abort_flag, 4);
+          for (uint32_t t = 0; ok && *pv_issued < j - 1; ++t)
+            if (t > TC_WAIT_LIMIT || *abort_flag) { *abort_flag = 8; atomicCAS(&tl_attn_tc_error, 0, 8); ok = false; }
+          if (!ok) break;
+        }
+        ok = tc_mbar_wait_parked(&k_full[j % TC_KSLOTS], (uint32_t)(j / TC_KSLOTS) & 1u, abort_flag, 3);
         if (!ok) break;
         tc_fence_after();
-        issue_pv(i - 1);
-      }
-      tc_fence_after();
-      const uint32_t ka = tc_smem_u32(kv_s + (size_t)s * TC_STAGE_BYTES);
+        const uint32_t ka = k_lo + (uint32_t)(j % TC_KSLOTS) * (TC_K_BYTES >> 4);
+        const uint32_t acc = tmem_base + (uint32_t)(j & 1) * PAGE;
 #pragma unroll
-      for (int kk = 0; kk < HEAD_DIM / 16; ++kk) {
-        const uint32_t sub = kk >> 2, within = (kk & 3) * 2;   // 32 bytes per step inside a 64-column box
-        tc_umma(tmem_base, tc_desc(qa + sub * (TC_Q * 128)) + within, tc_desc(ka + sub * (PAGE * 128)) + within,
-                idesc_s, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < HEAD_DIM / 16; ++kk) {
+          // 32 bytes per step inside a 64-column box; the boxes of Q and of K lie one after another
+          const uint32_t q_off = (uint32_t)(kk >> 2) * ((TC_Q * 128) >> 4) + (kk & 3) * 2;
+          const uint32_t k_off = (uint32_t)(kk >> 2) * ((PAGE * 128) >> 4) + (kk & 3) * 2;
+          tc_umma(acc, desc_of(q_lo + q_off), desc_of(ka + k_off), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[j & 1]);
       }
-      tc_commit(s_full);
-    }
-    if (ok) ok = tc_mbar_wait(p_full, (uint32_t)(n_pg - 1) & 1u, abort_flag, 4);
-    if (ok) {
-      tc_fence_after();
-      issue_pv(n_pg - 1);
+    } else {
+      // O (+)= P(j) . V(j)
+      for (int j = 0; j < n_pg && ok; ++j) {
+        ok = tc_mbar_wait_parked(&v_full[j % TC_VSLOTS], (uint32_t)(j / TC_VSLOTS) & 1u, abort_flag, 3) &&
+             tc_mbar_wait_parked(&p_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag, 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t va = v_lo + (uint32_t)(j % TC_VSLOTS) * (TC_V_BYTES >> 4);
+        const uint32_t pa = TC_P_IN_K ? p_lo + (uint32_t)(j % TC_KSLOTS) * (TC_K_BYTES >> 4) : p_lo;
+#pragma unroll
+        for (int k = 0; k < PAGE / 16; ++k)
+          tc_umma(tmem_o, desc_of(pa + k * 2), desc_of(va + k * 2), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&k_empty[j % TC_KSLOTS]);   // the page's slabs are free once these have read them
+        tc_commit(&v_empty[j % TC_VSLOTS]);
+        tc_commit(o_done);
+        *pv_issued = j + 1;
+      }
     }
   } else if (warp < 4) {
     // ---- softmax: one thread per query row
@@ -260,12 +354,12 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
     for (int i = 0; i < n_pg; ++i) {
-      ok = tc_mbar_wait(s_full, (uint32_t)i & 1u, abort_flag, 5);
+      ok = tc_mbar_wait(&s_full[i & 1], (uint32_t)(i >> 1) & 1u, abort_flag, 5);
       if (!ok) break;
       tc_fence_after();
       uint32_t sa[32], sb[32];
-      tc_ld32(t_s, sa);
-      tc_ld32(t_s + 32, sb);
+      tc_ld32(t_s + (uint32_t)(i & 1) * PAGE, sa);
+      tc_ld32(t_s + (uint32_t)(i & 1) * PAGE + 32, sb);
       tc_wait_ld();
       const int key0 = (ps + i) * PAGE;
       // a page that every row of this warp sees whole needs no mask (all but the pages on the
@@ -274,7 +368,7 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
       float mx = -INFINITY;
       if (whole) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
+        for (int j = 0; j < 32; ++j) mx = tc_max3(mx, __uint_as_float(sa[j]), __uint_as_float(sb[j]));
         mx *= scale_log2;
       } else {
 #pragma unroll
@@ -284,7 +378,7 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
           const float vb = (valid_row && kb_ >= lo && kb_ <= pos) ? __uint_as_float(sb[j]) : -INFINITY;
           sa[j] = __float_as_uint(va);
           sb[j] = __float_as_uint(vb);
-          mx = fmaxf(mx, fmaxf(va, vb));
+          mx = tc_max3(mx, va, vb);
         }
         mx *= scale_log2;   // the scale is positive; -inf stays -inf
       }
@@ -295,25 +389,36 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
       const float ref = m_new == -INFINITY ? 0.0f : m_new;
       const float alpha = exp2f(m - ref);
       m = m_new;
-      float sum = 0.0f;
+      // two scores at a time: one packed multiply-add for the exponents, one packed add for
+      // the sums (fma.rn.f32x2, add.rn.f32x2); the exponentials themselves are single
       uint32_t pk[32];   // the row of P as bfloat16 pairs: 64 keys = 128 bytes
+      const uint64_t scale2 = tc_pack2(scale_log2, scale_log2), nref2 = tc_pack2(-ref, -ref);
+      uint64_t sum_a = tc_pack2(0.0f, 0.0f), sum_b = sum_a;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const float p0 = exp2f(fmaf(__uint_as_float(sa[2 * j]), scale_log2, -ref));
-        const float p1 = exp2f(fmaf(__uint_as_float(sa[2 * j + 1]), scale_log2, -ref));
-        const float p2 = exp2f(fmaf(__uint_as_float(sb[2 * j]), scale_log2, -ref));
-        const float p3 = exp2f(fmaf(__uint_as_float(sb[2 * j + 1]), scale_log2, -ref));
-        sum += (p0 + p1) + (p2 + p3);
+        float x0, x1, x2, x3;
+        tc_unpack2(tc_fma2(tc_pack2(__uint_as_float(sa[2 * j]), __uint_as_float(sa[2 * j + 1])), scale2, nref2), x0, x1);
+        tc_unpack2(tc_fma2(tc_pack2(__uint_as_float(sb[2 * j]), __uint_as_float(sb[2 * j + 1])), scale2, nref2), x2, x3);
+        const float p0 = tc_ex2(x0), p1 = tc_ex2(x1), p2 = tc_ex2(x2), p3 = tc_ex2(x3);
+        sum_a = tc_add2(sum_a, tc_pack2(p0, p1));
+        sum_b = tc_add2(sum_b, tc_pack2(p2, p3));
         pk[j] = pack_bf16(p0, p1);
         pk[16 + j] = pack_bf16(p2, p3);
       }
+      float sum, sum_hi;
+      tc_unpack2(tc_add2(sum_a, sum_b), sum, sum_hi);
+      sum += sum_hi;
       l = l * alpha + sum;
-      if (i > 0) {
-        // P(i-1) . V(i-1) has finished: O is stable and the P tile may be written again
+      // O is touched only when some row's reference moved, and only then (or when P has one
+      // buffer of its own, which P(i-1) . V(i-1) still reads) the softmax waits for the products.
+      // The wait cannot mistake an older phase for this one: S(i), whose end this thread has
+      // seen, was issued after P(i-2) . V(i-2).
+      const bool rescale = i > 0 && __any_sync(0xffffffffu, alpha != 1.0f);
+      if (i > 0 && (rescale || !TC_P_IN_K)) {
         ok = tc_mbar_wait(o_done, (uint32_t)(i - 1) & 1u, abort_flag, 6);
         if (!ok) break;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {   // some row's reference moved: rescale O
+        if (rescale) {
 #pragma unroll
           for (int c = 0; c < HEAD_DIM; c += 32) {
             uint32_t ov[32];
@@ -327,7 +432,7 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
         }
       }
       // row r of the P tile: 8 chunks of 16 bytes, chunk c at (c ^ (r & 7))
-      const uint32_t prow = (TC_P_IN_K ? tc_smem_u32(kv_s + (size_t)(i % TC_STAGES) * TC_STAGE_BYTES)
+      const uint32_t prow = (TC_P_IN_K ? tc_smem_u32(k_s + (size_t)(i % TC_KSLOTS) * TC_K_BYTES)
                                        : tc_smem_u32(p_s)) + (uint32_t)r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c)
@@ -336,7 +441,7 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
                      : "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core's reads
       tc_fence_before();
-      tc_mbar_arrive(p_full);
+      tc_mbar_arrive(&p_full[i & 1]);
     }
     if (ok) ok = tc_mbar_wait(o_done, (uint32_t)(n_pg - 1) & 1u, abort_flag, 7);
     if (ok) {
@@ -435,7 +540,7 @@ extern "C" int FN(tl_attn_prefill_tc)(const void* q, long long T, const void* k_
   if (!tc_make_map(&tq, q, T, (long long)nh * HEAD_DIM, TC_Q)) return -2;
   if (!tc_make_map(&tk, k_pages, n_pages * nkv * PAGE, HEAD_DIM, PAGE)) return -2;
   if (!tc_make_map(&tv, v_pages, n_pages * nkv * HEAD_DIM, PAGE, HEAD_DIM)) return -2;
-  const size_t smem = 1024 + TC_Q_BYTES + TC_P_BYTES + (size_t)TC_STAGES * TC_STAGE_BYTES + 256;
+  const size_t smem = TC_SMEM_BYTES;   // the last 256 bytes hold the barriers
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(FN(attn_prefill_tc_kernel),
@@ -456,3 +561,4 @@ extern "C" int FN(tl_attn_tc_take_error)() {
   if (v) cudaMemcpyToSymbol(tl_attn_tc_error, &zero, sizeof(int));
   return v;
 }
+
