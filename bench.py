@@ -278,7 +278,10 @@ def main() -> int:
         "gpu_launches": launches,
         "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
                     "ms": round(pre_ms, 3),
-                    "frac": round(flops / (pre_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(flops / (pre_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+                    "peak_tflops": peaks["bf16_tflops"],
+                    "frac_of_sustained": (round(flops / (pre_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12), 4)
+                                          if peaks.get("bf16_tflops_sustained") else None)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": points,
