@@ -131,6 +131,47 @@ __device__ __forceinline__ u64 blk_scan(u64 v, SampleShared& sm, u64* total) {
   return v + off;
 }
 
+// Histogram updates of a whole warp: lanes that hit the same bin are found with match_any and
+// one of them adds for all (most logits share their leading bits, so plain atomics would
+// queue a thousand threads on two or three bins).  Every lane of the warp must call these;
+// `bin` < 0 takes no part.
+__device__ __forceinline__ void warp_count(uint32_t* cnt, int bin) {
+  const unsigned peers = __match_any_sync(0xffffffffu, bin);
+  if (bin >= 0 && (int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[bin], (uint32_t)__popc(peers));
+}
+__device__ __forceinline__ void warp_count_weight(uint32_t* cnt, u64* wsum, int bin, u64 w) {
+  const unsigned peers = __match_any_sync(0xffffffffu, bin);
+  // the weights have 41 bits: three sums of 16-bit (and 9-bit) pieces cannot overflow 32 bits
+  const uint32_t a = __reduce_add_sync(peers, (uint32_t)(w & 0xffffull));
+  const uint32_t b = __reduce_add_sync(peers, (uint32_t)((w >> 16) & 0xffffull));
+  const uint32_t c = __reduce_add_sync(peers, (uint32_t)(w >> 32));
+  if (bin >= 0 && (int)(threadIdx.x & 31) == __ffs(peers) - 1) {
+    atomicAdd(&cnt[bin], (uint32_t)__popc(peers));
+    atomicAdd(&wsum[bin], (u64)a + ((u64)b << 16) + ((u64)c << 32));
+  }
+}
+
+// Calls f(i, row[i], valid) for every entry of the row, every lane of a warp the same number
+// of times (entries past the end come with valid = false).  Four consecutive entries per
+// thread and 16-byte loads when the row allows it, so that a pass is not a chain of single
+// loads that each wait for L2.
+template <typename F>
+__device__ __forceinline__ void for_each_entry(const float* row, int V, F f) {
+  const int tid = threadIdx.x;
+  const int V4 = (((uintptr_t)row & 15) == 0) ? (V & ~3) : 0;
+  for (int i0 = 0; i0 < V4; i0 += blockDim.x * 4) {
+    const int i = i0 + tid * 4;
+    const bool valid = i < V4;
+    const float4 x = valid ? *reinterpret_cast<const float4*>(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    f(i, x.x, valid); f(i + 1, x.y, valid); f(i + 2, x.z, valid); f(i + 3, x.w, valid);
+  }
+  for (int i0 = V4; i0 < V; i0 += blockDim.x) {
+    const int i = i0 + tid;
+    const bool valid = i < V;
+    f(i, valid ? row[i] : 0.0f, valid);
+  }
+}
+
 struct RowView {
   const float* row;
   int V;
@@ -146,7 +187,7 @@ struct RowView {
   int p_cut;
 };
 
-__device__ __forceinline__ float z_of(const RowView& rv, int i) { return rv.row[i] / rv.T; }
+__device__ __forceinline__ float z_from(const RowView& rv, float x) { return x / rv.T; }
 
 __device__ __forceinline__ bool kept_k(const RowView& rv, float z, int i) {
   if (!rv.use_k) return true;
@@ -158,24 +199,57 @@ __device__ __forceinline__ u64 fix_of(const RowView& rv, float z) {
   return (u64)(expf(z - rv.m) * FIX_ONE);
 }
 
-// Index of the `need`-th entry (1-based, in index order) for which pred holds.
-template <typename Pred>
-__device__ int nth_in_order(int V, int need, SampleShared& sm, Pred pred) {
+// The first index, in index order, at which the running sum of weight(i) exceeds `target`
+// (`fallback` if the whole sum does not).  Each thread takes SCAN_E consecutive entries per
+// round, so a round of the block covers 8192 entries with one scan.
+#define SCAN_E 8
+template <typename Weight>
+__device__ int first_exceeding(const float* row, int V, u64 target, SampleShared& sm, int fallback,
+                               Weight weight) {
   u64 carry = 0;
-  int found = V - 1;
-  for (int base = 0; base < V; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    const u64 f = (i < V && pred(i)) ? 1ull : 0ull;
+  int found = fallback;
+  const bool vec = ((uintptr_t)row & 15) == 0;
+  for (int base = 0; base < V; base += blockDim.x * SCAN_E) {
+    const int i0 = base + threadIdx.x * SCAN_E;
+    float x[SCAN_E];
+    if (vec && i0 + SCAN_E <= V) {
+      const float4 a = *reinterpret_cast<const float4*>(row + i0), b = *reinterpret_cast<const float4*>(row + i0 + 4);
+      x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < SCAN_E; ++e) x[e] = i0 + e < V ? row[i0 + e] : 0.0f;
+    }
+    u64 w[SCAN_E], mine = 0;
+#pragma unroll
+    for (int e = 0; e < SCAN_E; ++e) {
+      w[e] = i0 + e < V ? weight(i0 + e, x[e]) : 0ull;
+      mine += w[e];
+    }
     u64 total;
-    const u64 inc = blk_scan(f, sm, &total) + carry;
-    if (f && inc == (u64)need) sm.bcast_int[0] = i;
-    const bool done = carry < (u64)need && carry + total >= (u64)need;
+    const u64 inc = blk_scan(mine, sm, &total) + carry;
+    u64 run = inc - mine;
+    if (mine && inc > target && run <= target) {   // the crossing lies in this thread's entries
+#pragma unroll
+      for (int e = 0; e < SCAN_E; ++e) {
+        const bool before = run <= target;
+        run += w[e];
+        if (before && run > target) sm.bcast_int[0] = i0 + e;
+      }
+    }
+    const bool done = carry + total > target;
     carry += total;
     __syncthreads();
     if (done) { found = sm.bcast_int[0]; break; }
   }
   __syncthreads();
   return found;
+}
+
+// Index of the `need`-th entry (1-based, in index order) for which pred holds.
+template <typename Pred>
+__device__ int nth_in_order(const float* row, int V, int need, SampleShared& sm, Pred pred) {
+  return first_exceeding(row, V, (u64)(need - 1), sm, V - 1,
+                         [&](int i, float x) { return pred(i, x) ? 1ull : 0ull; });
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
@@ -195,10 +269,10 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
 
   // ---- max of the scaled logits
   float m = -INFINITY;
-  for (int i = tid; i < V; i += blockDim.x) {
-    const float z = z_of(rv, i);
-    if (z == z) m = fmaxf(m, z);
-  }
+  for_each_entry(rv.row, V, [&](int, float x, bool valid) {
+    const float z = z_from(rv, x);
+    if (valid && z == z) m = fmaxf(m, z);
+  });
   rv.m = blk_max(m, sm);
 
   // ---- top-k: key of the k-th largest scaled logit by radix selection
@@ -208,10 +282,10 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     for (int shift = 24; shift >= 0; shift -= 8) {
       for (int b = tid; b < 256; b += blockDim.x) sm.cnt[b] = 0u;
       __syncthreads();
-      for (int i = tid; i < V; i += blockDim.x) {
-        const uint32_t k = float_key(z_of(rv, i));
-        if ((k & mask) == prefix) atomicAdd(&sm.cnt[(k >> shift) & 255u], 1u);
-      }
+      for_each_entry(rv.row, V, [&](int, float x, bool valid) {   // whole warps: see warp_count
+        const uint32_t k = float_key(z_from(rv, x));
+        warp_count(sm.cnt, (valid && (k & mask) == prefix) ? (int)((k >> shift) & 255u) : -1);
+      });
       __syncthreads();
       if (tid == 0) {
         int rem = remaining, b = 255;
@@ -232,16 +306,16 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     // `remaining` entries equal to the threshold are kept, lowest indices first
     const uint32_t thr = prefix;
     const RowView rvc = rv;
-    rv.k_cut = nth_in_order(V, remaining, sm,
-                            [&](int i) { return float_key(z_of(rvc, i)) == thr; });
+    rv.k_cut = nth_in_order(rv.row, V, remaining, sm,
+                            [&](int, float x) { return float_key(z_from(rvc, x)) == thr; });
   }
 
   // ---- sum of the kept fixed-point weights
   u64 part = 0;
-  for (int i = tid; i < V; i += blockDim.x) {
-    const float z = z_of(rv, i);
-    if (z == z && kept_k(rv, z, i)) part += fix_of(rv, z);
-  }
+  for_each_entry(rv.row, V, [&](int i, float x, bool valid) {
+    const float z = z_from(rv, x);
+    if (valid && z == z && kept_k(rv, z, i)) part += fix_of(rv, z);
+  });
   u64 S;
   blk_scan(part, sm, &S);
   __syncthreads();
@@ -255,16 +329,16 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     for (int shift = 40; shift >= 0; shift -= 8) {
       for (int b = tid; b < 256; b += blockDim.x) { sm.cnt[b] = 0u; sm.wsum[b] = 0ull; }
       __syncthreads();
-      for (int i = tid; i < V; i += blockDim.x) {
-        const float z = z_of(rv, i);
-        if (!(z == z) || !kept_k(rv, z, i)) continue;
-        const u64 w = fix_of(rv, z);
-        if ((w & mask) == prefix) {
-          const int b = (int)((w >> shift) & 255ull);
-          atomicAdd(&sm.cnt[b], 1u);
-          atomicAdd(&sm.wsum[b], w);
+      for_each_entry(rv.row, V, [&](int i, float x, bool valid) {   // whole warps: see warp_count
+        int b = -1;
+        u64 w = 0;
+        const float z = z_from(rv, x);
+        if (valid && z == z && kept_k(rv, z, i)) {
+          w = fix_of(rv, z);
+          if ((w & mask) == prefix) b = (int)((w >> shift) & 255ull);
         }
-      }
+        warp_count_weight(sm.cnt, sm.wsum, b, w);
+      });
       __syncthreads();
       if (tid == 0) {
         u64 acc = above;
@@ -291,8 +365,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
     }
     const RowView rvc = rv;
     const u64 thr = prefix;
-    rv.p_cut = nth_in_order(V, need, sm, [&](int i) {
-      const float z = z_of(rvc, i);
+    rv.p_cut = nth_in_order(rv.row, V, need, sm, [&](int i, float x) {
+      const float z = z_from(rvc, x);
       return z == z && kept_k(rvc, z, i) && fix_of(rvc, z) == thr;
     });
     S = above + (u64)need * prefix;
@@ -303,26 +377,14 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, float temperature
   r = r < 0.0f ? 0.0f : (r >= 1.0f ? 0.99999994f : r);
   u64 target = (u64)((double)r * (double)S);
   if (target >= S) target = S ? S - 1ull : 0ull;
-  u64 carry = 0;
-  int chosen = -1;
-  for (int base = 0; base < V; base += blockDim.x) {
-    const int i = base + tid;
-    u64 w = 0;
-    if (i < V) {
-      const float z = z_of(rv, i);
-      if (z == z && kept_k(rv, z, i)) {
-        w = fix_of(rv, z);
-        if (rv.use_p && !(w > rv.p_thr || (w == rv.p_thr && i <= rv.p_cut))) w = 0;
-      }
-    }
-    u64 total;
-    const u64 inc = blk_scan(w, sm, &total) + carry;
-    if (w && inc > target && inc - w <= target) sm.bcast_int[0] = i;
-    const bool done = carry + total > target;
-    carry += total;
-    __syncthreads();
-    if (done) { chosen = sm.bcast_int[0]; break; }
-  }
+  const RowView rvd = rv;
+  const int chosen = first_exceeding(rv.row, V, target, sm, -1, [&](int i, float x) {
+    const float z = z_from(rvd, x);
+    if (!(z == z) || !kept_k(rvd, z, i)) return 0ull;
+    const u64 w = fix_of(rvd, z);
+    if (rvd.use_p && !(w > rvd.p_thr || (w == rvd.p_thr && i <= rvd.p_cut))) return 0ull;
+    return w;
+  });
   if (tid == 0) out[blockIdx.x] = chosen >= 0 ? chosen : V - 1;  // the reference's fallback, :237
 }
 
