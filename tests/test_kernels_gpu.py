@@ -299,7 +299,7 @@ def test_attention_decode_far_key_stands_out(use_tma):
                                    (1000, 2500, 136), (2048, 4096, 512), (1024, 5000, 2048),
                                    (100, 512, 4096), (200, 384, 2048), (300, 640, 4096),
                                    (300, 4096, 1024), (130, 6100, 768), (70, 4096, 4096),
-                                   (300, 256, 14336), (200, 384, 8192)])
+                                   (300, 256, 14336), (200, 384, 8192), (513, 384, 256), (140, 256, 512)])
 def test_gemm_tensor_core(M, N, K):
     from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16
     g = GemmBf16.get()

@@ -700,7 +700,7 @@ __device__ __forceinline__ bool epilogue_all(bool ok) {
   return r != 0;
 }
 
-#define PAIR_BN 256       // tokens per pair tile
+#define PAIR_BN 256       // most tokens per pair tile; a launch picks a multiple of 32 up to this
 #define PAIR_STAGE 32768  // bytes per stage and block: 128 operand rows + 128 token rows
 #define PAIR_XCHG 8192    // SiLU-gate exchange: two buffers of 2 x 8 x 64 floats
 #define PAIR_MAX_BLOCKS 160
@@ -716,13 +716,15 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_x, const GemmArgs args, int m_tiles,
-                    int total_tiles, int splits) {
+                    int total_tiles, int splits, int bn) {
   constexpr uint32_t A_BYTES = 128 * TILE_K * 2;
   constexpr uint32_t ACC_COLS = PAIR_BN;
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
   constexpr int PAIR_N = SWIGLU ? 128 : 256;   // output columns per pair tile
-  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PAIR_BN >> 3) << 17) |
-                             ((uint32_t)(256 >> 4) << 24);
+  // tokens per tile `bn`: the N of the instruction; each block holds bn / 2 token rows
+  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) |
+                         ((uint32_t)(256 >> 4) << 24);
+  const uint32_t stage_tx = 2u * (A_BYTES + (uint32_t)bn * 64u);   // bytes both blocks load per stage
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -761,14 +763,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     uint32_t it = 0;
     for (int item = pair; item < total_items; item += n_pairs) {
       const int tile = item / splits, split = item % splits;
-      const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * PAIR_BN;
+      const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * bn;
       const int kb_b = split * args.kb_per_split, kb_e = min(kb_total, kb_b + args.kb_per_split);
       for (int kb = kb_b; kb < kb_e; ++kb, ++it) {
         const int s = it % stages;
         const uint32_t ph = (it / stages) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) { item = total_items; break; }
         uint8_t* st = smem + (size_t)s * PAIR_STAGE;
-        if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * PAIR_STAGE);
+        if (rank == 0) mbar_expect_tx(&full_bar[s], stage_tx);
         const uint32_t bar = mapa_u32(smem_u32(&full_bar[s]), 0);
         const int k = kb * TILE_K;
         if (SWIGLU) {
@@ -778,7 +780,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
           tma_load_2d_pair(st, &tm_w, bar, k, n0 + 128 * (int)rank);
         }
         if (!waited) { pdl_wait(); waited = true; }
-        tma_load_2d_pair(st + A_BYTES, &tm_x, bar, k, m0 + 128 * (int)rank);
+        tma_load_2d_pair(st + A_BYTES, &tm_x, bar, k, m0 + (bn >> 1) * (int)rank);
       }
     }
   } else if (warp == 5 && lane == 0 && rank == 0) {
@@ -805,7 +807,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
 #pragma unroll
         for (int k = 0; k < TILE_K / UMMA_K; ++k) {
           const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);
-          umma_bf16_pair(acc, da + adv, db + adv, IDESC, (kb > kb_b || k > 0) ? 1u : 0u);
+          umma_bf16_pair(acc, da + adv, db + adv, idesc, (kb > kb_b || k > 0) ? 1u : 0u);
         }
         umma_commit_pair(&empty_bar[s]);
       }
@@ -820,7 +822,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
     uint32_t local = 0;
     for (int item = pair; item < total_items; item += n_pairs, ++local) {
       const int tile = item / splits, split = item % splits;
-      const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * PAIR_BN;
+      const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * bn;
       const uint32_t buf = local & 1u;
       const bool merge = splits > 1 && split == 0;   // this pair writes C
       bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1u, abort_flag, 3);
@@ -840,7 +842,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * ACC_COLS;
       if (split > 0) {
-        for (int c0 = 0; c0 < PAIR_BN; c0 += 16) {
+        for (int c0 = 0; c0 < bn; c0 += 16) {
           uint32_t r[16];
           tmem_ld16(taddr + c0, r);
           tmem_ld_wait();
@@ -856,7 +858,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
         // writes tokens 0-7 of each 16, the up half tokens 8-15
         const int col = row & 63, up_half = row >> 6;
         const int n = n0 + 64 * (int)rank + col;
-        for (int c0 = 0, i = 0; c0 < PAIR_BN; c0 += 16, ++i) {
+        for (int c0 = 0, i = 0; c0 < bn; c0 += 16, ++i) {
           uint32_t r[16];
           tmem_ld16(taddr + c0, r);
           tmem_ld_wait();
@@ -890,10 +892,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
         // 64 values of C are fetched at once: four round trips to memory per tile, which
         // matters for the last tile, whose epilogue nothing hides
         const int n = n0 + 128 * (int)rank + row;
-        for (int c0 = 0; c0 < PAIR_BN; c0 += 64) {
+        for (int c0 = 0; c0 < bn; c0 += 64) {
           float prev[64];
           float* cf = (float*)args.C + (size_t)(m0 + c0) * args.ldc + n;
-          const int valid = args.M - (m0 + c0);
+          const int valid = min(args.M - (m0 + c0), bn - c0);   // the tile's own tokens only
 #pragma unroll
           for (int j = 0; j < 64; ++j) prev[j] = (n < args.N && j < valid) ? cf[(size_t)j * args.ldc] : 0.0f;
           float part[64];   // the other splits' sums, added in split order, then to the accumulator
@@ -921,7 +923,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
         }
       } else {
         const int n = n0 + 128 * (int)rank + row;
-        for (int c0 = 0; c0 < PAIR_BN; c0 += 16) {
+        for (int c0 = 0; c0 < bn; c0 += 16) {
           uint32_t r[16];
           tmem_ld16(taddr + c0, r);
           tmem_ld_wait();
@@ -1079,12 +1081,12 @@ static int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, GemmA
 
 // The pair kernel: clusters of two blocks, as many as the GPU holds at once.
 template <bool SWIGLU>
-static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int want_splits,
+static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int want_splits, int bn,
                        cudaStream_t stream) {
   const int stages = 6;
   a.stages = stages;
   const size_t smem = 1024 + (size_t)stages * PAIR_STAGE + 2048 + PAIR_XCHG;
-  const int m_tiles = (a.M + PAIR_BN - 1) / PAIR_BN;
+  const int m_tiles = (a.M + bn - 1) / bn;
   const int pair_n = SWIGLU ? 128 : 256;
   const int total = m_tiles * ((a.N + pair_n - 1) / pair_n);
   cudaLaunchConfig_t cfg = {};
@@ -1121,7 +1123,7 @@ static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a,
   splits = (kb_total + a.kb_per_split - 1) / a.kb_per_split;   // no empty split
   const int items = total * splits;
   cfg.gridDim = dim3(2 * (items < max_pairs ? items : max_pairs));
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU>, tw, tx, a, m_tiles, total, splits);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU>, tw, tx, a, m_tiles, total, splits, bn);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -1190,7 +1192,10 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   static const int pair_on = getenv("TL_NO_PAIR") ? 0 : 1;
   const int pairs = num_sms / 2;
   const int pair_n = swiglu ? 128 : 256;
-  const long long tiles_p = (long long)((N + pair_n - 1) / pair_n) * ((M + PAIR_BN - 1) / PAIR_BN);
+  // token tiles of equal width, a multiple of 32 (300 tokens: two tiles of 160, not 256 + 44)
+  const int pair_m_tiles = (M + PAIR_BN - 1) / PAIR_BN;
+  const int pair_bn = ((M + pair_m_tiles - 1) / pair_m_tiles + 31) / 32 * 32;
+  const long long tiles_p = (long long)((N + pair_n - 1) / pair_n) * pair_m_tiles;
   // K split over idle pairs: the merge of s partial tiles costs about 16 + 24 (s - 1)
   // K-blocks' time (measured)
   int pair_splits = 1;
@@ -1205,11 +1210,11 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   if (use_pair && pair_on) {
     CUtensorMap pw, px;
     if (make_map(&pw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, swiglu ? 64 : 128) &&
-        make_map(&px, X, M, K, ldx, 128)) {
+        make_map(&px, X, M, K, ldx, pair_bn / 2)) {
       GemmArgs p = {};
       p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.mode = mode;
-      const int rc = swiglu ? launch_pair<true>(pw, px, p, pair_splits, stream)
-                            : launch_pair<false>(pw, px, p, pair_splits, stream);
+      const int rc = swiglu ? launch_pair<true>(pw, px, p, pair_splits, pair_bn, stream)
+                            : launch_pair<false>(pw, px, p, pair_splits, pair_bn, stream);
       if (rc != -2) return rc;
     }
   }
