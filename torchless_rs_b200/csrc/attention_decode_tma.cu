@@ -113,9 +113,10 @@ FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __gri
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_wait();
-  pdl_launch_dependents();
 
+  // Lengths and page tables were copied to the device before the step's first kernel, and every
+  // page but a sequence's last was filled by earlier steps: only the last page (it holds the
+  // newest token's keys and values) and the queries come from the kernels just before this one.
   const int len = seq_len[b];
   const int lo = (window > 0 && len - window > 0) ? len - window : 0;
   const int* table = page_table + (size_t)seq_slot[b] * table_stride;
@@ -137,8 +138,13 @@ FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __gri
     td_tma_load_2d(st + K_BYTES, &tm_v, &full_bar[s], 0, slab * HEAD_DIM);
     return true;
   };
+  int ahead = 0;   // pages requested before the wait for the earlier kernels
   if (threadIdx.x == 0)
-    for (int i = 0; i < TD_STAGES - 1 && i < n_pg; ++i) issue(i);
+    for (; ahead < TD_STAGES - 1 && ahead < n_pg && ps + ahead < last_page; ++ahead) issue(ahead);
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x == 0)
+    for (int i = ahead; i < TD_STAGES - 1 && i < n_pg; ++i) issue(i);
 
   // query fragments: rows are the query heads of this kv head
   uint32_t qa[NCHUNK][4], qb[NCHUNK][4];
