@@ -362,6 +362,48 @@ def test_attention_prefill_bf16(nh, nkv, hd, window, variant):
             assert torch.allclose(got[tkn], ref, **_attn_tol(dtype)), f"seq {b} pos {pos}"
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,lens,new", [
+    (30, 3, 64, None, [399, 373, 159], [260, 333, 132]),
+    (30, 3, 64, 100, [274, 319], [274, 157]),
+    (20, 2, 128, None, [384, 369, 490], [243, 321, 393])])
+def test_attention_prefill_tc_many_blocks_repeated(nh, nkv, hd, window, lens, new):
+    """Many heads per key/value head, so that many blocks of the tensor-core prefill kernel run
+    side by side on the same pages, and the same launch several times: a page's contribution
+    once went missing now and then when a softmax warp rescaled the output while the product
+    of the page before was still under way."""
+    from torchless_rs_b200.csrc.attention_bf16 import AttentionBf16
+    att = AttentionBf16.get(hd)
+    dtype = torch.bfloat16
+    pc = Paged(lens, nkv, hd, dtype, 1000 + nh + hd)
+    B, T, G = len(lens), sum(new), nh // nkv
+    q = _rand((T, nh * hd), dtype, 1001)
+    starts = [0]
+    for n in new:
+        starts.append(starts[-1] + n)
+    seq_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    ref = torch.empty((T, nh, hd), dtype=torch.float64, device=DEV)
+    for b in range(B):
+        k = pc.k[b].to(DEV).double().repeat_interleave(G, dim=1)     # [n, nh, hd]
+        v = pc.v[b].to(DEV).double().repeat_interleave(G, dim=1)
+        qq = q[starts[b]:starts[b + 1]].view(new[b], nh, hd).double()
+        pos = torch.arange(lens[b] - new[b], lens[b], device=DEV)
+        keys = torch.arange(lens[b], device=DEV)
+        seen = keys[None, :] <= pos[:, None]
+        if window:
+            seen &= keys[None, :] > pos[:, None] - window
+        sc = torch.einsum("qhd,khd->hqk", qq, k) * scale
+        p = torch.softmax(sc.masked_fill(~seen[None], float("-inf")), -1)
+        ref[starts[b]:starts[b + 1]] = torch.einsum("hqk,khd->qhd", p, v)
+    for rep in range(8):
+        out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        att.prefill(q, pc.k_pages, pc.v_pages, out, seq_start, seq_len, pc.seq_slot, pc.table, B,
+                    max(new), nh, nkv, window, scale, variant="tc")
+        assert att.take_error() == 0
+        assert torch.allclose(out.double().view(T, nh, hd), ref, **_attn_tol(dtype)), f"repetition {rep}"
+
+
 @pytest.mark.parametrize("kernel", ["prefill_bf16_tc", "prefill_bf16_tma", "prefill_bf16_plain", "generic_bf16",
                                     "generic_f32"])
 def test_attention_far_key_stands_out_in_every_kernel(kernel):

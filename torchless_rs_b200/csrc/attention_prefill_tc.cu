@@ -6,19 +6,22 @@
 //                                S in tensor memory
 //   softmax     four warps, one thread per query row: tcgen05.ld of the row, mask, running
 //               maximum and sum in 32-bit (no shuffles: a row lives in one thread), P
-//               rounded to bfloat16 into shared memory; O is rescaled in tensor memory only
-//               when some row's maximum moved
-//   O[128, hd] += P . V          tcgen05.mma, P from shared memory, the page's transposed V
-//                                slab as the K-major B operand
+//               rounded to bfloat16 back into tensor memory (tcgen05.st, over the S buffer);
+//               O is rescaled in tensor memory only when some row's maximum moved
+//   O[128, hd] += P . V          tcgen05.mma with P as the A operand in tensor memory and
+//                                the page's transposed V slab as the K-major B operand
 // S has two buffers in tensor memory: Q . K^T of page i + 1 is issued (by a thread of its
 // own) before the softmax of page i has ended, and P . V of page i (issued by another thread)
 // runs under the softmax of page i + 1, so the softmax warps rarely wait for a product.  Pages
 // come by TMA, K slabs one page ahead of V slabs.  What was measured with clock64() stamps in
-// one block: per page the softmax takes about 1100 cycles of arithmetic (bound by the
-// 16 exponentials a cycle of an SM when two blocks share it), 450 for the P stores and the
-// proxy fence, 200 for the barrier; issuing one tcgen05.mma costs its thread about 80 cycles.
-// Arithmetic as in attention_prefill_bf16.cu (reference: src/model/modules/attention.rs:88-121, src/model/modules/flash_attention.rs:
-// 101-136, window of src/model/models/gpt_oss.rs:168-176).  Head sizes 64 and 128.
+// one block while P still went through shared memory: per page the softmax takes about 1100
+// cycles of arithmetic (bound by the 16 exponentials a cycle of an SM when two blocks share
+// it), 450 for the P stores and the proxy fence that the tensor core's reads of shared memory
+// need (what moving P to tensor memory saves), 200 for the barrier; issuing one tcgen05.mma
+// costs its thread about 80 cycles.
+// Arithmetic as in attention_prefill_bf16.cu (reference: src/model/modules/attention.rs:88-121,
+// src/model/modules/flash_attention.rs:101-136, window of src/model/models/gpt_oss.rs:168-176).
+// Head sizes 64 and 128.
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the block records a code in
 // tl_attn_tc_error, stops, frees its tensor memory and returns.
@@ -44,9 +47,10 @@
 #define TC_V_BYTES (HEAD_DIM * PAGE * 2)
 // P[128 queries, 64 keys] is as large as the K slab of a page when the head size is 128; it is then
 // written over that slab, which Q.K^T has finished with, and needs no buffer of its own
-#define TC_P_IN_K (HEAD_DIM == 128)
-#define TC_P_BYTES (TC_P_IN_K ? 0 : TC_Q * PAGE * 2)
-#define TC_SMEM_BYTES (TC_Q_BYTES + TC_P_BYTES + TC_KSLOTS * TC_K_BYTES + TC_VSLOTS * TC_V_BYTES + 256)
+// P goes back into tensor memory, over the first 32 columns of the S buffer it was computed
+// from (two bfloat16 per column), and P . V takes its A operand from there: no shared memory
+// for P and no proxy fence between the softmax's stores and the tensor core's reads.
+#define TC_SMEM_BYTES (TC_Q_BYTES + TC_KSLOTS * TC_K_BYTES + TC_VSLOTS * TC_V_BYTES + 256)
 #define TC_WAIT_LIMIT (1u << 22)
 #define TC_TMEM_COLS 256   // S twice (64 columns each), then O (HEAD_DIM columns)
 
@@ -95,6 +99,16 @@ __device__ __forceinline__ void tc_umma(uint32_t tmem_d, uint64_t da, uint64_t d
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       :
       : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// The same with the A operand in tensor memory (row = lane, two bfloat16 per column).
+__device__ __forceinline__ void tc_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(acc)
       : "memory");
 }
 // A wait that lets the hardware park the thread (up to about a microsecond per try) instead of
@@ -202,8 +216,7 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
   extern __shared__ __align__(1024) uint8_t tc_smem_raw[];
   uint8_t* smem = tc_smem_raw;
   uint8_t* q_s = smem;
-  uint8_t* p_s = q_s + TC_Q_BYTES;
-  uint8_t* k_s = p_s + TC_P_BYTES;
+  uint8_t* k_s = q_s + TC_Q_BYTES;
   uint8_t* v_s = k_s + TC_KSLOTS * TC_K_BYTES;
   uint64_t* q_full = (uint64_t*)(v_s + TC_VSLOTS * TC_V_BYTES);
   uint64_t* k_full = q_full + 1;
@@ -213,9 +226,9 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
   uint64_t* s_full = v_empty + TC_VSLOTS;   // [2], one per S buffer
   uint64_t* p_full = s_full + 2;             // [2]
   uint64_t* o_done = p_full + 2;
-  uint32_t* tmem_slot = (uint32_t*)(o_done + 1);
+  uint64_t* pv_done = o_done + 1;            // [2]: P . V of the page whose P lies in S buffer u is done
+  uint32_t* tmem_slot = (uint32_t*)(pv_done + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-  volatile int* pv_issued = abort_flag + 1;   // pages whose P . V the second issuer has issued
 
   const int b = blockIdx.z, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -237,8 +250,9 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
     for (int s = 0; s < TC_VSLOTS; ++s) { tc_mbar_init(&v_full[s], 1); tc_mbar_init(&v_empty[s], 1); }
     for (int u = 0; u < 2; ++u) { tc_mbar_init(&s_full[u], 1); tc_mbar_init(&p_full[u], 128); }
     tc_mbar_init(o_done, 1);
+    tc_mbar_init(&pv_done[0], 1);
+    tc_mbar_init(&pv_done[1], 1);
     *abort_flag = 0;
-    *pv_issued = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -297,18 +311,14 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
     auto desc_of = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
     const uint32_t q_lo = lo_of(tc_smem_u32(q_s));
     const uint32_t k_lo = lo_of(tc_smem_u32(k_s)), v_lo = lo_of(tc_smem_u32(v_s));
-    const uint32_t p_lo = TC_P_IN_K ? k_lo : lo_of(tc_smem_u32(p_s));
     bool ok = true;
     if (warp == 5) {
       // S(j) = Q . K(j)^T into buffer j & 1, up to two pages ahead of the softmax
       ok = tc_mbar_wait_parked(q_full, 0, abort_flag, 2);
       for (int j = 0; j < n_pg && ok; ++j) {
         if (j >= 2) {
-          // the buffer is free when the softmax of page j - 2 has read it; and the other issuer
-          // must have seen that same phase of the barrier before the next one can complete
-          ok = tc_mbar_wait_parked(&p_full[j & 1], (uint32_t)((j - 2) >> 1) & 1u, abort_flag, 4);
-          for (uint32_t t = 0; ok && *pv_issued < j - 1; ++t)
-            if (t > TC_WAIT_LIMIT || *abort_flag) { *abort_flag = 8; atomicCAS(&tl_attn_tc_error, 0, 8); ok = false; }
+          // the buffer holds P(j - 2) until P(j - 2) . V(j - 2) has read it
+          ok = tc_mbar_wait_parked(&pv_done[j & 1], (uint32_t)((j - 2) >> 1) & 1u, abort_flag, 4);
           if (!ok) break;
         }
         ok = tc_mbar_wait_parked(&k_full[j % TC_KSLOTS], (uint32_t)(j / TC_KSLOTS) & 1u, abort_flag, 3);
@@ -324,6 +334,7 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
           tc_umma(acc, desc_of(q_lo + q_off), desc_of(ka + k_off), idesc_s, kk > 0 ? 1u : 0u);
         }
         tc_commit(&s_full[j & 1]);
+        tc_commit(&k_empty[j % TC_KSLOTS]);   // nothing else reads the K slab
       }
     } else {
       // O (+)= P(j) . V(j)
@@ -333,14 +344,13 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
         if (!ok) break;
         tc_fence_after();
         const uint32_t va = v_lo + (uint32_t)(j % TC_VSLOTS) * (TC_V_BYTES >> 4);
-        const uint32_t pa = TC_P_IN_K ? p_lo + (uint32_t)(j % TC_KSLOTS) * (TC_K_BYTES >> 4) : p_lo;
 #pragma unroll
-        for (int k = 0; k < PAGE / 16; ++k)
-          tc_umma(tmem_o, desc_of(pa + k * 2), desc_of(va + k * 2), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&k_empty[j % TC_KSLOTS]);   // the page's slabs are free once these have read them
-        tc_commit(&v_empty[j % TC_VSLOTS]);
+        for (int k = 0; k < PAGE / 16; ++k)   // 16 keys = 8 columns of P
+          tc_umma_ts(tmem_o, tmem_base + (uint32_t)(j & 1) * PAGE + k * 8, desc_of(va + k * 2), idesc_o,
+                     (j > 0 || k > 0) ? 1u : 0u);
         tc_commit(o_done);
-        *pv_issued = j + 1;
+        tc_commit(&pv_done[j & 1]);
+        tc_commit(&v_empty[j % TC_VSLOTS]);
       }
     }
   } else if (warp < 4) {
@@ -409,16 +419,15 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
       tc_unpack2(tc_add2(sum_a, sum_b), sum, sum_hi);
       sum += sum_hi;
       l = l * alpha + sum;
-      // O is touched only when some row's reference moved, and only then (or when P has one
-      // buffer of its own, which P(i-1) . V(i-1) still reads) the softmax waits for the products.
-      // The wait cannot mistake an older phase for this one: S(i), whose end this thread has
-      // seen, was issued after P(i-2) . V(i-2).
-      const bool rescale = i > 0 && __any_sync(0xffffffffu, alpha != 1.0f);
-      if (i > 0 && (rescale || !TC_P_IN_K)) {
+      // O is touched only when some row's reference moved.  Every warp waits for P(i-1) . V(i-1)
+      // on every page all the same (by now it has nearly always ended): a warp that looked at
+      // this barrier only now and then could take the phase of P(i-3) . V(i-3) for this one,
+      // because nothing orders the arrival of page i - 2 on it before this warp gets here.
+      if (i > 0) {
         ok = tc_mbar_wait(o_done, (uint32_t)(i - 1) & 1u, abort_flag, 6);
         if (!ok) break;
         tc_fence_after();
-        if (rescale) {
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
           for (int c = 0; c < HEAD_DIM; c += 32) {
             uint32_t ov[32];
@@ -431,15 +440,8 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
           tc_wait_st();
         }
       }
-      // row r of the P tile: 8 chunks of 16 bytes, chunk c at (c ^ (r & 7))
-      const uint32_t prow = (TC_P_IN_K ? tc_smem_u32(k_s + (size_t)(i % TC_KSLOTS) * TC_K_BYTES)
-                                       : tc_smem_u32(p_s)) + (uint32_t)r * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (uint32_t)((c ^ (r & 7)) << 4)),
-                     "r"(pk[4 * c]), "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
-                     : "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core's reads
+      tc_st32(t_s + (uint32_t)(i & 1) * PAGE, pk);   // this lane's row of P, keys 2c and 2c + 1 in column c
+      tc_wait_st();
       tc_fence_before();
       tc_mbar_arrive(&p_full[i & 1]);
     }
