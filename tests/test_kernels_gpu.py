@@ -329,6 +329,25 @@ def test_gemm_tensor_core(M, N, K):
     assert g.take_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 4096, 14336), (140, 1024, 8192), (2048, 1024, 1024), (8, 4096, 4096)])
+def test_gemm_tensor_core_back_to_back(M, N, K):
+    """The same accumulating product many times in a row without a synchronisation between the
+    launches, which overlap at their edges: the partial tiles and flags of a K split over pairs
+    of SMs, and the cluster reductions of the few-token kernel, must not leak from one launch
+    into the next."""
+    from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16
+    g = GemmBf16.get()
+    a = _rand((M, K), torch.bfloat16, 300)
+    ws = [_rand((N, K), torch.bfloat16, 301 + i, 1.0 / math.sqrt(K)) for i in range(3)]
+    ref = sum(a.double() @ w.double().T for w in ws) * 6
+    for trial in range(2):
+        c = torch.zeros((M, N), dtype=torch.float32, device=DEV)
+        for it in range(18):
+            assert g.run(a, ws[it % 3], c, 1)
+        assert torch.allclose(c.double(), ref, rtol=1e-3, atol=1e-3 * float(ref.abs().max())), f"trial {trial}"
+    assert g.take_error() == 0
+
+
 @pytest.mark.parametrize("variant", ["tc", "tma", "plain"])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, None), (8, 2, 128, 100), (4, 4, 64, 33),
                                                (3, 1, 32, None), (6, 3, 64, 64)])
