@@ -169,6 +169,19 @@ __device__ __forceinline__ float ld_remote_f32(uint32_t local_saddr, uint32_t ra
   return v;
 }
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float4 ld_remote_f32x4(uint32_t local_saddr, uint32_t rank) {
+  uint32_t raddr;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_saddr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(raddr) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
 // ---------------------------------------------------------------------------
@@ -371,6 +384,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const int rank = (int)cluster_rank();
       const bool accum = args.mode == MODE_ACCUM_F32 && !SWIGLU;
       int my_cols = 0;
+      // Without the folded rotation: a warp takes one column (token) at a time, each lane four
+      // consecutive rows of it, so that partial tiles come over in 16-byte loads and C goes out
+      // in 16-byte (bfloat16: 8-byte) stores; two columns per turn keep more loads in flight.
+      const bool vec4 = !args.rope_on && (args.ldc & 3) == 0 && (args.N & 3) == 0 &&
+                        ((uintptr_t)args.C & 15) == 0 && (!args.xw_out || ((uintptr_t)args.xw_out & 7) == 0);
+      if (vec4) {
+        const int n4 = n0 + 4 * lane;
+        const bool live4 = n4 < args.N && !*abort_flag;   // N is a multiple of 4: all four or none
+        float nw4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (args.xw_out && live4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            nw4[e] = args.nw_is_f32 ? ((const float*)args.nw)[n4 + e]
+                                    : __bfloat162float(((const __nv_bfloat16*)args.nw)[n4 + e]);
+        }
+        for (int k0 = warp; rank + k0 * splits < cols; k0 += 8) {
+          float4 v[2], u[2], prev[2];
+          int cc[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int c = rank + (k0 + 4 * h) * splits;
+            cc[h] = c < cols ? c : -1;
+            v[h] = u[h] = prev[h] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (cc[h] >= 0 && accum && live4)
+              prev[h] = *reinterpret_cast<const float4*>((const float*)args.C + (size_t)(m0 + c) * args.ldc + n4);
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (cc[h] < 0) continue;
+            for (int sp = 0; sp < splits; ++sp) {
+              const float4 a = ld_remote_f32x4(red_s + (uint32_t)(cc[h] * TILE_N + 4 * lane) * 4u, (uint32_t)sp);
+              v[h].x += a.x; v[h].y += a.y; v[h].z += a.z; v[h].w += a.w;
+              if (SWIGLU) {
+                const float4 b = ld_remote_f32x4(red_s + (uint32_t)((BN + cc[h]) * TILE_N + 4 * lane) * 4u, (uint32_t)sp);
+                u[h].x += b.x; u[h].y += b.y; u[h].z += b.z; u[h].w += b.w;
+              }
+            }
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (cc[h] < 0) continue;
+            const int c = cc[h];
+            float val[4] = {v[h].x, v[h].y, v[h].z, v[h].w}, up[4] = {u[h].x, u[h].y, u[h].z, u[h].w};
+            const float pv[4] = {prev[h].x, prev[h].y, prev[h].z, prev[h].w};
+            if (args.ss_in) {
+              const float sc = rinv_c[c];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { val[e] *= sc; up[e] *= sc; }
+            }
+            const size_t idx = (size_t)(m0 + c) * args.ldc + n4;
+            float sq = 0.0f;
+            if (live4) {
+              if (SWIGLU) {
+                uint2 o;
+                o.x = pack_bf16x2(silu_f(val[0]) * up[0], silu_f(val[1]) * up[1]);
+                o.y = pack_bf16x2(silu_f(val[2]) * up[2], silu_f(val[3]) * up[3]);
+                *reinterpret_cast<uint2*>((__nv_bfloat16*)args.C + idx) = o;
+              } else if (args.mode == MODE_STORE_F32) {
+                *reinterpret_cast<float4*>((float*)args.C + idx) = make_float4(val[0], val[1], val[2], val[3]);
+              } else if (accum) {
+                float cn[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) cn[e] = pv[e] + val[e];
+                *reinterpret_cast<float4*>((float*)args.C + idx) = make_float4(cn[0], cn[1], cn[2], cn[3]);
+                if (args.xw_out) {
+                  uint2 o;
+                  o.x = pack_bf16x2(cn[0] * nw4[0], cn[1] * nw4[1]);
+                  o.y = pack_bf16x2(cn[2] * nw4[2], cn[3] * nw4[3]);
+                  *reinterpret_cast<uint2*>(args.xw_out + (size_t)(m0 + c) * args.N + n4) = o;
+                  sq = (cn[0] * cn[0] + cn[1] * cn[1]) + (cn[2] * cn[2] + cn[3] * cn[3]);
+                }
+              } else {
+                uint2 o;
+                o.x = pack_bf16x2(val[0], val[1]);
+                o.y = pack_bf16x2(val[2], val[3]);
+                *reinterpret_cast<uint2*>((__nv_bfloat16*)args.C + idx) = o;
+              }
+            }
+            if (args.xw_out) {   // the tile's 128 rows of this column lie in this one warp
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+              if (lane == 0) args.ss_out[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = sq;
+            }
+          }
+        }
+      } else {
       // columns rank, rank + splits, ... in groups of 8, so that the loads of a group (old C,
       // partials of every split) are in flight together
       for (int cb = rank; cb < cols; cb += 8 * splits) {
@@ -460,6 +559,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           const float t = ((ssw[threadIdx.x] + ssw[64 + threadIdx.x]) + ssw[128 + threadIdx.x]) + ssw[192 + threadIdx.x];
           args.ss_out[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = t;
         }
+      }
       }
     }
     cluster_sync_all();   // nobody leaves while others still read its shared memory
