@@ -801,7 +801,10 @@ __device__ __forceinline__ bool epilogue_all(bool ok) {
 }
 
 #define PAIR_BN 256       // most tokens per pair tile; a launch picks a multiple of 32 up to this
-#define PAIR_STAGE 32768  // bytes per stage and block: 128 operand rows + 128 token rows
+#define PAIR_K 128        // K elements per stage: two 64-element (128-byte) sub-tiles per operand, so that the
+                          // issuing thread's fixed cost per stage (barrier wait, commit, loop) is paid half as often
+#define PAIR_SUB 16384    // bytes of one sub-tile slot: 128 rows of 128 bytes
+#define PAIR_STAGE 65536  // bytes per stage and block: [A k0][A k1][B k0][B k1]
 #define PAIR_XCHG 8192    // SiLU-gate exchange: two buffers of 2 x 8 x 64 floats
 #define PAIR_MAX_BLOCKS 160
 
@@ -817,14 +820,13 @@ __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_x, const GemmArgs args, int m_tiles,
                     int total_tiles, int splits, int bn) {
-  constexpr uint32_t A_BYTES = 128 * TILE_K * 2;
   constexpr uint32_t ACC_COLS = PAIR_BN;
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
   constexpr int PAIR_N = SWIGLU ? 128 : 256;   // output columns per pair tile
   // tokens per tile `bn`: the N of the instruction; each block holds bn / 2 token rows
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) |
                          ((uint32_t)(256 >> 4) << 24);
-  const uint32_t stage_tx = 2u * (A_BYTES + (uint32_t)bn * 64u);   // bytes both blocks load per stage
+  const uint32_t stage_tx = 2u * 2u * (PAIR_SUB + (uint32_t)bn * 64u);   // bytes both blocks load per stage
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -838,7 +840,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
   float* xchg = (float*)(smem + (size_t)stages * PAIR_STAGE + 2048);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb_total = (args.K + TILE_K - 1) / TILE_K;
+  const int kb_total = (args.K + PAIR_K - 1) / PAIR_K;
   const uint32_t rank = cluster_rank();          // 0 issues the instructions
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   // work item = (tile, split); with splits > 1 the grid holds every item at once
@@ -860,32 +862,38 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
   if (warp == 4 && lane == 0) {
     // ---- TMA producer of this block's halves; the bytes count at the first block's barrier
     bool waited = false;
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
     for (int item = pair; item < total_items; item += n_pairs) {
       const int tile = item / splits, split = item % splits;
       const int n0 = (tile / m_tiles) * PAIR_N, m0 = (tile % m_tiles) * bn;
       const int kb_b = split * args.kb_per_split, kb_e = min(kb_total, kb_b + args.kb_per_split);
-      for (int kb = kb_b; kb < kb_e; ++kb, ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1u;
+      for (int kb = kb_b; kb < kb_e; ++kb) {
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) { item = total_items; break; }
         uint8_t* st = smem + (size_t)s * PAIR_STAGE;
         if (rank == 0) mbar_expect_tx(&full_bar[s], stage_tx);
         const uint32_t bar = mapa_u32(smem_u32(&full_bar[s]), 0);
-        const int k = kb * TILE_K;
-        if (SWIGLU) {
-          tma_load_2d_pair(st, &tm_w, bar, k, n0 + 64 * (int)rank);
-          tma_load_2d_pair(st + A_BYTES / 2, &tm_w, bar, k, args.N + n0 + 64 * (int)rank);
-        } else {
-          tma_load_2d_pair(st, &tm_w, bar, k, n0 + 128 * (int)rank);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {   // the two 64-element halves of the stage's K range (past K: zeros)
+          const int k = kb * PAIR_K + h * TILE_K;
+          if (SWIGLU) {
+            tma_load_2d_pair(st + h * PAIR_SUB, &tm_w, bar, k, n0 + 64 * (int)rank);
+            tma_load_2d_pair(st + h * PAIR_SUB + PAIR_SUB / 2, &tm_w, bar, k, args.N + n0 + 64 * (int)rank);
+          } else {
+            tma_load_2d_pair(st + h * PAIR_SUB, &tm_w, bar, k, n0 + 128 * (int)rank);
+          }
         }
         if (!waited) { pdl_wait(); waited = true; }
-        tma_load_2d_pair(st + A_BYTES, &tm_x, bar, k, m0 + (bn >> 1) * (int)rank);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_2d_pair(st + (2 + h) * PAIR_SUB, &tm_x, bar, kb * PAIR_K + h * TILE_K, m0 + (bn >> 1) * (int)rank);
+        if (++s == stages) { s = 0; ph ^= 1u; }
       }
     }
   } else if (warp == 5 && lane == 0 && rank == 0) {
     // ---- MMA issuer of the pair
-    uint32_t it = 0, local = 0;
+    uint32_t local = 0, ph = 0;
+    int s = 0;
     bool ok = true;
     for (int item = pair; item < total_items && ok; item += n_pairs, ++local) {
       const int split = item % splits;
@@ -895,21 +903,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc = tmem_base + buf * ACC_COLS;
-      for (int kb = kb_b; kb < kb_e; ++kb, ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1u;
+      for (int kb = kb_b; kb < kb_e; ++kb) {
         ok = mbar_wait(&full_bar[s], ph, abort_flag, 2);
         if (!ok) break;
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + (size_t)s * PAIR_STAGE);
         const uint64_t da = smem_desc_k128(sa);
-        const uint64_t db = smem_desc_k128(sa + A_BYTES);
+        const uint64_t db = smem_desc_k128(sa + 2 * PAIR_SUB);
 #pragma unroll
-        for (int k = 0; k < TILE_K / UMMA_K; ++k) {
-          const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);
+        for (int k = 0; k < PAIR_K / UMMA_K; ++k) {
+          // 32 bytes per step inside a sub-tile, then the next sub-tile
+          const uint64_t adv = (uint64_t)((k >> 2) * (PAIR_SUB >> 4) + (k & 3) * 2);
           umma_bf16_pair(acc, da + adv, db + adv, idesc, (kb > kb_b || k > 0) ? 1u : 0u);
         }
         umma_commit_pair(&empty_bar[s]);
+        if (++s == stages) { s = 0; ph ^= 1u; }
       }
       if (ok) umma_commit_pair(&acc_full[buf]);
     }
@@ -1183,7 +1191,7 @@ static int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, GemmA
 template <bool SWIGLU>
 static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int want_splits, int bn,
                        cudaStream_t stream) {
-  const int stages = 6;
+  const int stages = 3;
   a.stages = stages;
   const size_t smem = 1024 + (size_t)stages * PAIR_STAGE + 2048 + PAIR_XCHG;
   const int m_tiles = (a.M + bn - 1) / bn;
@@ -1216,7 +1224,7 @@ static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a,
   }
   if (max_pairs <= 0) return -2;
   // K split over several pairs per tile only while every (tile, split) runs at once
-  const int kb_total = (a.K + TILE_K - 1) / TILE_K;
+  const int kb_total = (a.K + PAIR_K - 1) / PAIR_K;
   int splits = want_splits;
   while (splits > 1 && (long long)total * splits > max_pairs) --splits;
   a.kb_per_split = (kb_total + splits - 1) / splits;
