@@ -222,9 +222,16 @@ template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                const GemmArgs args) {
+  // A stage holds KS sub-tiles of 64 K-elements (128 bytes) per operand: two where one weight
+  // matrix is read, so that the issuing thread pays its fixed cost per stage (barrier wait,
+  // commit, loop: some 400 cycles) once per eight instructions; the SiLU-gate's two matrices
+  // make eight instructions per 64 elements already.  Layout: [A sub-tiles][B sub-tiles].
+  constexpr int KS = SWIGLU ? 1 : 2;
+  constexpr int KSTEP = TILE_K * KS;
   constexpr uint32_t A_BYTES = TILE_N * TILE_K * 2;
   constexpr uint32_t B_BYTES = BN * TILE_K * 2;
-  constexpr uint32_t STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
+  constexpr uint32_t STAGE_BYTES = KS * (A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES);
+  constexpr uint32_t B_OFF = KS * A_BYTES * (SWIGLU ? 2 : 1);
   constexpr uint32_t ACC_COLS = BN * (SWIGLU ? 2 : 1);
   constexpr uint32_t TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;   // a power of two >= 32
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
@@ -243,7 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * TILE_N, m0 = blockIdx.y * BN;
   const int splits = gridDim.z, split = blockIdx.z;
-  const int kb_total = (args.K + TILE_K - 1) / TILE_K;
+  const int kb_total = (args.K + KSTEP - 1) / KSTEP;
   const int kb0 = split * args.kb_per_split;
   const int kb1 = min(kb0 + args.kb_per_split, kb_total);
   const int n_kb = kb1 - kb0;
@@ -266,50 +273,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // ---- TMA producer.  The weights do not depend on earlier kernels, so the tiles of the
     // first stages are requested before the wait for those kernels; the activations after it.
     const int pre = n_kb < stages ? n_kb : stages;
+    auto load_w = [&](uint8_t* st, uint64_t* bar, int kb) {
+#pragma unroll
+      for (int h = 0; h < KS; ++h) {
+        const int k = kb * KSTEP + h * TILE_K;   // past K the tile is filled with zeros
+        tma_load_2d(st + h * A_BYTES, &tm_w, bar, k, n0);
+        if (SWIGLU) tma_load_2d(st + A_BYTES, &tm_w, bar, k, args.N + n0);
+      }
+    };
+    auto load_x = [&](uint8_t* st, uint64_t* bar, int kb) {
+#pragma unroll
+      for (int h = 0; h < KS; ++h)
+        tma_load_2d(st + B_OFF + h * B_BYTES, &tm_x, bar, kb * KSTEP + h * TILE_K, m0);
+    };
     for (int i = 0; i < pre; ++i) {
-      uint8_t* st = smem + (size_t)i * STAGE_BYTES;
       mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-      const int k = (kb0 + i) * TILE_K;
-      tma_load_2d(st, &tm_w, &full_bar[i], k, n0);
-      if (SWIGLU) tma_load_2d(st + A_BYTES, &tm_w, &full_bar[i], k, args.N + n0);
+      load_w(smem + (size_t)i * STAGE_BYTES, &full_bar[i], kb0 + i);
     }
     pdl_wait();
-    for (int i = 0; i < pre; ++i) {
-      uint8_t* st = smem + (size_t)i * STAGE_BYTES;
-      tma_load_2d(st + A_BYTES * (SWIGLU ? 2 : 1), &tm_x, &full_bar[i], (kb0 + i) * TILE_K, m0);
-    }
+    for (int i = 0; i < pre; ++i) load_x(smem + (size_t)i * STAGE_BYTES, &full_bar[i], kb0 + i);
+    int s = pre == stages ? 0 : pre;
+    uint32_t ph = pre == stages ? 1u : 0u;   // phase of the stage's next use
     for (int i = pre; i < n_kb; ++i) {
-      const int s = i % stages;
-      const uint32_t ph = (uint32_t)(i / stages) & 1u;
       if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, 1)) break;
       uint8_t* st = smem + (size_t)s * STAGE_BYTES;
       mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-      const int k = (kb0 + i) * TILE_K;
-      tma_load_2d(st, &tm_w, &full_bar[s], k, n0);
-      if (SWIGLU) tma_load_2d(st + A_BYTES, &tm_w, &full_bar[s], k, args.N + n0);
-      tma_load_2d(st + A_BYTES * (SWIGLU ? 2 : 1), &tm_x, &full_bar[s], k, m0);
+      load_w(st, &full_bar[s], kb0 + i);
+      load_x(st, &full_bar[s], kb0 + i);
+      if (++s == stages) { s = 0; ph ^= 1u; }
     }
   } else if (warp == 5 && lane == 0) {
     // ---- MMA issuer
     bool ok = true;
+    int s = 0;
+    uint32_t ph = 0;
     for (int i = 0; i < n_kb && ok; ++i) {
-      const int s = i % stages;
-      const uint32_t ph = (uint32_t)(i / stages) & 1u;
       ok = mbar_wait(&full_bar[s], ph, abort_flag, 2);
       if (!ok) break;
       tc_fence_after();
       const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
       const uint64_t da = smem_desc_k128(sa);
       const uint64_t da2 = smem_desc_k128(sa + A_BYTES);
-      const uint64_t db = smem_desc_k128(sa + A_BYTES * (SWIGLU ? 2 : 1));
+      const uint64_t db = smem_desc_k128(sa + B_OFF);
 #pragma unroll
-      for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+      for (int k = 0; k < KSTEP / UMMA_K; ++k) {
         const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-        const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);   // 32 bytes per step
-        umma_bf16(tmem_base, da + adv, db + adv, IDESC, acc);
-        if (SWIGLU) umma_bf16(tmem_base + BN, da2 + adv, db + adv, IDESC, acc);
+        // 32 bytes per step inside a sub-tile, then the next sub-tile
+        const uint64_t adv_a = (uint64_t)((k >> 2) * (A_BYTES >> 4) + (k & 3) * 2);
+        const uint64_t adv_b = (uint64_t)((k >> 2) * (B_BYTES >> 4) + (k & 3) * 2);
+        umma_bf16(tmem_base, da + adv_a, db + adv_b, IDESC, acc);
+        if (SWIGLU) umma_bf16(tmem_base + BN, da2 + adv_a, db + adv_b, IDESC, acc);
       }
       umma_commit(&empty_bar[s]);   // the stage is free once these instructions have read it
+      if (++s == stages) { s = 0; ph ^= 1u; }
     }
     if (ok) umma_commit(acc_bar);
   } else if (warp < 4) {
@@ -1122,7 +1138,7 @@ static bool make_map(CUtensorMap* map, const void* ptr, long long rows, long lon
 template <int BN, bool SWIGLU>
 static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int splits,
                   size_t smem_budget, cudaStream_t stream) {
-  const size_t stage = (size_t)TILE_N * TILE_K * 2 * (SWIGLU ? 2 : 1) + (size_t)BN * TILE_K * 2;
+  const size_t stage = (SWIGLU ? 1 : 2) * ((size_t)TILE_N * TILE_K * 2 * (SWIGLU ? 2 : 1) + (size_t)BN * TILE_K * 2);
   int stages = (int)((smem_budget - 1024 - 2048) / stage);
   stages = stages > 8 ? 8 : stages;
   if (stages < 2) return -2;
@@ -1275,25 +1291,28 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = (M + bn - 1) / bn;
   const long long tiles = (long long)n_tiles * m_tiles;
   const int kb_total = (K + TILE_K - 1) / TILE_K;
+  // stages of the few-token kernel: 128 K-elements, 64 with the SiLU-gate's two matrices
+  const int kstep64 = swiglu ? 1 : 2;
+  const int kb_np = (K + TILE_K * kstep64 - 1) / (TILE_K * kstep64);
   // two blocks per SM fit while the token tile is small
   const bool two_per_sm = bn <= 64;
   // small token tiles leave room for the blocks of the next kernel, which fetch their first
   // weight tiles while this kernel drains
-  const size_t budget = !two_per_sm ? 224 * 1024 : (!swiglu && bn <= 32) ? 80 * 1024 : 112 * 1024;
+  const size_t budget = !two_per_sm ? 224 * 1024 : (!swiglu && bn <= 32) ? 88 * 1024 : 112 * 1024;
   const long long slots = (long long)num_sms * (two_per_sm ? 2 : 1);
   int splits = 1;
   if (tiles < slots && (two_per_sm || !ss_in)) {
     // a power of two (clusters of 3, 5, 6 or 7 blocks do not tile the GPCs evenly, and a
     // cluster that has to wait for a second wave doubles the kernel's time), as large as
     // keeps every block resident at once
-    while (splits * 2 <= MAX_SPLITS && tiles * splits * 2 <= slots && splits * 2 <= kb_total / 2)
+    while (splits * 2 <= MAX_SPLITS && tiles * splits * 2 <= slots && splits * 2 <= kb_np / 2)
       splits *= 2;
-    // token tiles of 128: the reduction of so wide a tile costs about 40 K-blocks' time
-    // (measured), so the split has to save more than that
-    if (!two_per_sm && (kb_total + splits - 1) / splits + 40 >= kb_total) splits = 1;
+    // token tiles of 128: the reduction of so wide a tile costs about as much as 40 K-blocks
+    // of 64 elements (measured), so the split has to save more than that
+    if (!two_per_sm && ((kb_np + splits - 1) / splits) * kstep64 + 40 >= kb_total) splits = 1;
   }
-  int kb_per_split = (kb_total + splits - 1) / splits;
-  splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
+  int kb_per_split = (kb_np + splits - 1) / splits;
+  splits = (kb_np + kb_per_split - 1) / kb_per_split;   // no empty split
   // Many tokens: the persistent kernels with two accumulators.
   const bool persistent = M > 128 && !ss_in;
   if (persistent) bn = swiglu ? 128 : 256;
