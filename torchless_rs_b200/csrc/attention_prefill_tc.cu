@@ -230,14 +230,15 @@ FN(attn_prefill_tc_kernel)(const __grid_constant__ CUtensorMap tm_q, const __gri
   uint32_t* tmem_slot = (uint32_t*)(pv_done + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
-  const int b = blockIdx.z, h = blockIdx.y;
+  const int b = blockIdx.z, h = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_wait();
   pdl_launch_dependents();
   const int tok0 = seq_start[b];
   const int n_new = seq_start[b + 1] - tok0;
-  // the last queries of a sequence see the most keys: their blocks come first in the grid
-  const int blk0 = (int)(gridDim.x - 1 - blockIdx.x) * TC_Q;
+  // the last queries of a sequence see the most keys: their blocks come first in the grid, for all
+  // heads (the fastest index) before any shorter block, so that the launch ends with the short ones
+  const int blk0 = (int)(gridDim.y - 1 - blockIdx.y) * TC_Q;
   if (blk0 >= n_new) return;   // before any tensor memory is taken
   if (tc_smem_u32(tc_smem_raw) & 1023u) {   // see above; nothing has been allocated yet
     if (threadIdx.x == 0) atomicCAS(&tl_attn_tc_error, 0, 9);
@@ -550,7 +551,9 @@ extern "C" int FN(tl_attn_prefill_tc)(const void* q, long long T, const void* k_
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((max_new + TC_Q - 1) / TC_Q, nh, B);
+  const int q_tiles = (max_new + TC_Q - 1) / TC_Q;
+  if (q_tiles > 65535) return -2;
+  dim3 grid(nh, q_tiles, B);
   return tl_launch(FN(attn_prefill_tc_kernel), grid, dim3(TC_THREADS), smem, stream, tq, tk, tv,
                    (__nv_bfloat16*)out, seq_start, seq_len, seq_slot, page_table, table_stride, nh, nkv,
                    window, scale * 1.4426950408889634f);
