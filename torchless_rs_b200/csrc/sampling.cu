@@ -68,10 +68,63 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
   }
 }
 
+// The same with several blocks per row, for the few rows of a decode step (one block per row
+// leaves most SMs idle and takes as long as its one chain of loads).  A block folds its part
+// of the row into one 64-bit word per row with atomicMax: key in the high half, the
+// complemented index in the low half, so that among equal keys the lowest index wins.  The
+// block that finishes a row last writes the result and clears the row's word and counter for
+// the next launch (they are static: launches on one stream at a time).
+#define ARGMAX_ROWS 4096
+#define ARGMAX_THREADS 256
+__device__ unsigned long long tl_argmax_word[ARGMAX_ROWS];
+__device__ unsigned int tl_argmax_count[ARGMAX_ROWS];
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_parts_kernel(const float* __restrict__ logits, int ld, int V, int per_block, int* __restrict__ out) {
+  __shared__ unsigned long long sw[ARGMAX_THREADS / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.y;
+  const float* row = logits + (size_t)r * ld;
+  const int begin = blockIdx.x * per_block, end = min(V, begin + per_block);
+  unsigned long long best = 0ull;
+#pragma unroll 4
+  for (int i = begin + threadIdx.x; i < end; i += ARGMAX_THREADS) {
+    const unsigned long long w = ((unsigned long long)float_key(row[i]) << 32) | (uint32_t)~(uint32_t)i;
+    best = w > best ? w : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long ow = __shfl_xor_sync(0xffffffffu, best, o);
+    best = ow > best ? ow : best;
+  }
+  if ((threadIdx.x & 31) == 0) sw[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < ARGMAX_THREADS / 32; ++w) best = sw[w] > best ? sw[w] : best;
+    atomicMax(&tl_argmax_word[r], best);
+    __threadfence();
+    if (atomicAdd(&tl_argmax_count[r], 1u) == gridDim.x - 1) {   // every part of the row is in
+      __threadfence();
+      const unsigned long long w = atomicExch(&tl_argmax_word[r], 0ull);
+      const uint32_t idx = ~(uint32_t)(w & 0xffffffffull);
+      out[r] = (w != 0ull && idx < (uint32_t)V) ? (int)idx : 0;
+      tl_argmax_count[r] = 0u;
+    }
+  }
+}
+
 extern "C" int tl_argmax(const float* logits, int ld, int rows, int V, int* out,
                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return -1;
+  // few rows: spread each over several blocks, about 148 blocks in all
+  const int parts = rows >= 64 ? 1 : min(16, max(1, min(148 / rows, (V + 2047) / 2048)));
+  if (parts > 1 && rows <= ARGMAX_ROWS) {
+    const int per_block = (V + parts - 1) / parts;
+    return tl_launch(argmax_parts_kernel, dim3(parts, rows), dim3(ARGMAX_THREADS), 0, stream, logits, ld, V,
+                     per_block, out);
+  }
   return tl_launch(argmax_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, out);
 }
 
