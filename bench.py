@@ -248,7 +248,7 @@ def main() -> int:
         p_tps, p_ms, _, _ = decode_device_timed(model, b, k, 3, CONTEXT)
         points[f"decode_b{b}"] = round(p_tps, 1)
         points[f"decode_b{b}_ms"] = round(p_ms, 3)
-    pre_ms = prefill_timed(model, PREFILL_TOKENS)
+    pre_ms = prefill_timed(model, PREFILL_TOKENS, repeats=6)
     clocks.stop()
 
     step_bytes = wbytes + B * mean_ctx * kvb
