@@ -37,7 +37,7 @@
 #define TC_Q 128                         // queries per block
 // Two blocks per SM (one block's products overlap the other's softmax) leave each block room
 // for five page slabs beside its queries: three of K, whose page i + 1 is wanted one softmax
-// earlier than its V, and two of V.  K(i + 1) and V(i) take the slabs that P(i-2) . V(i-2) frees.
+// earlier than its V and which Q . K^T alone reads, and two of V, free again after P . V.
 #define TC_KSLOTS 3
 #define TC_VSLOTS 2
 #define TC_THREADS 224                   // warps 0-3 softmax, warp 4 TMA, warp 5 issues Q.K^T, warp 6 issues P.V
@@ -45,8 +45,6 @@
 #define TC_Q_BYTES (TC_Q * HEAD_DIM * 2)
 #define TC_K_BYTES (PAGE * HEAD_DIM * 2)
 #define TC_V_BYTES (HEAD_DIM * PAGE * 2)
-// P[128 queries, 64 keys] is as large as the K slab of a page when the head size is 128; it is then
-// written over that slab, which Q.K^T has finished with, and needs no buffer of its own
 // P goes back into tensor memory, over the first 32 columns of the S buffer it was computed
 // from (two bfloat16 per column), and P . V takes its A operand from there: no shared memory
 // for P and no proxy fence between the softmax's stores and the tensor core's reads.
