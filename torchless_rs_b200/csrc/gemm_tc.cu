@@ -6,10 +6,13 @@
 // a tile of BN rows of X (tokens) is its N operand, and the accumulator lies in tensor
 // memory as [128 weight rows][BN tokens].  So the same kernel serves one decoded token
 // per sequence (BN = 16: the weights stream through TMA at full width and the padding
-// costs nothing that matters) and prefill (BN = 256).  Operands come by TMA into
-// 128-byte-swizzled shared memory tiles of 64 K-elements; one thread issues the
-// instructions; four warps read the accumulator back with tcgen05.ld and write C, each
-// warp-store covering 32 consecutive columns of one row of C.
+// costs nothing that matters) and more tokens (up to BN = 256; from 129 tokens on the
+// kernel on pairs of SMs further down takes over).  Operands come by TMA into
+// 128-byte-swizzled shared memory tiles of 64 K-elements, one or two of them per operand
+// and stage; one thread issues the instructions (each costs it some 70 cycles, a stage's
+// barrier wait, commit and loop some 400, which is why a stage holds eight instructions);
+// four warps read the accumulator back with tcgen05.ld and write C, each warp-store
+// covering 32 consecutive columns of one row of C.
 //
 // When a product has too few tiles to fill the GPU (decode), K is split over
 // blockIdx.z and the blocks of one tile form a thread-block cluster.  Each block puts
@@ -741,7 +744,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w,
 // cluster share one instruction of 256 weight rows x 256 tokens: each block holds 128 of
 // the weight rows and 128 of the tokens in its shared memory and 128 rows of the
 // accumulator in its tensor memory, so a block fetches 32 KB per 64 K-elements where the
-// one-SM kernel fetches 48 KB, and six stages fit instead of four.  The first block of
+// one-SM kernel fetches 48 KB.  A stage holds 128 K-elements (64 KB, three stages).  The first block of
 // the pair issues the instructions; the barrier that says "stage filled" lives there and
 // counts the bytes of both blocks' TMA loads; the instruction's completion is signalled
 // to the "stage free" and "accumulator ready" barriers of both blocks at once.
