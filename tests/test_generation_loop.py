@@ -209,3 +209,25 @@ def test_ahead_with_sampling_uses_the_same_uniform_numbers():
                  max_batch=3, reader=reader, to_host=list)
         runs.append(dict(got))
     assert runs[0] == runs[1]
+
+
+def test_a_set_error_word_is_raised_and_cleared():
+    """A kernel library that gave up on a bounded wait leaves a nonzero error word; the check
+    that generation and replay make where they wait for results anyway raises it, once."""
+    from torchless_rs_b200.csrc import ops
+
+    word = {"v": 0}
+
+    def take():
+        v, word["v"] = word["v"], 0
+        return v
+
+    ops.register_error_word("toy_library", take)
+    try:
+        ops.check_kernel_errors()
+        word["v"] = 3
+        with pytest.raises(ops.KernelError, match="toy_library: code 3"):
+            ops.check_kernel_errors()
+        ops.check_kernel_errors()
+    finally:
+        ops._error_words.pop("toy_library")

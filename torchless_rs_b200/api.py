@@ -91,8 +91,10 @@ class Model:
             stop_ids = self.engine.spec.stop_token_ids
         if self._reader is None:
             self._reader = OverlappedReader()
-        return _generate(self.engine, self.sampler.select, prompts, max_tokens, params, stop_ids,
-                         seed, on_token, max_batch=max_batch, reader=self._reader)
+        results = _generate(self.engine, self.sampler.select, prompts, max_tokens, params, stop_ids,
+                            seed, on_token, max_batch=max_batch, reader=self._reader)
+        self.engine.check_kernels()
+        return results
 
     def step(self, slots, tokens, want="last"):
         return self.engine.step(slots, tokens, want)

@@ -10,7 +10,7 @@ from typing import Dict
 import torch
 
 from . import build
-from .ops import KernelError, _check, _need, _ptr, _stream
+from .ops import KernelError, _check, _need, _ptr, _stream, register_error_word
 
 FAST_HEAD_DIMS = (32, 64, 128)
 MAX_GROUP = 16        # query heads per key/value head that one instruction's rows hold
@@ -68,6 +68,7 @@ class AttentionBf16:
                 self._tc_error.restype = c_int
                 self._tma_error = getattr(self.lib, f"tl_attn_tma_take_error_hd{head_dim}")
                 self._tma_error.restype = c_int
+                register_error_word(f"attn_bf16_hd{head_dim}", self.take_error)
 
     def take_error(self) -> int:
         """Nonzero if a TMA kernel gave up on a bounded wait since the last call (synchronises)."""

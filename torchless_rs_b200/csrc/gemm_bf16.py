@@ -8,7 +8,7 @@ from ctypes import byref, c_float, c_int, c_longlong, c_void_p
 import torch
 
 from . import build
-from .ops import KernelError, _check, _ptr, _stream
+from .ops import KernelError, _check, _ptr, _stream, register_error_word
 
 build.register_library("gemm_tc", ("gemm_tc.cu",), ())
 
@@ -35,6 +35,7 @@ class GemmBf16:
         self.lib = build.load_library("gemm_tc")
         self.lib.tl_gemm_tc.restype = c_int
         self.lib.tl_gemm_tc_take_error.restype = c_int
+        register_error_word("gemm_tc", self.take_error)
         self._scratch = {}
 
     def _scratch_for(self, device: torch.device):

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_void_p
-from typing import Optional
+from typing import Callable, Dict, Optional
 
 import torch
 
@@ -27,6 +27,22 @@ class KernelError(RuntimeError):
 
 
 _SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
+_error_words: Dict[str, Callable[[], int]] = {}
+
+
+def register_error_word(name: str, take: Callable[[], int]) -> None:
+    """A kernel library whose waits are bounded names the function that reads and clears
+    its error word (nonzero: a kernel gave up waiting, its results are not valid)."""
+    _error_words[name] = take
+
+
+def check_kernel_errors() -> None:
+    """Reads every registered error word (this synchronises the device) and raises if one is
+    set.  Callers use it where they wait for results anyway."""
+    bad = {name: code for name, code in ((n, take()) for n, take in _error_words.items()) if code}
+    if bad:
+        raise KernelError("a kernel ran out of a bounded wait, its results are not valid: " +
+                          ", ".join(f"{n}: code {c}" for n, c in bad.items()))
 _counter = {"launches": 0}
 
 

@@ -55,6 +55,11 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def check_kernels(self) -> None:
+        """Raises if a kernel gave up on one of its bounded waits since the last check (its
+        results are then wrong).  Synchronises the device."""
+        ops.check_kernel_errors()
+
     # ---- the step ----------------------------------------------------------------------
     def step(self, slots: Sequence[int], tokens: Optional[Sequence[Sequence[int]]] = None,
              want: Union[str, Sequence[Sequence[int]]] = "last",
