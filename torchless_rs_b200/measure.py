@@ -3,11 +3,18 @@
     python -m torchless_rs_b200.measure gemm M N K MODE [--iters I]
     python -m torchless_rs_b200.measure attn-decode BATCH CONTEXT [--iters I]
     python -m torchless_rs_b200.measure attn-prefill TOKENS [--iters I]
+    python -m torchless_rs_b200.measure step BATCH CONTEXT PREFILL_TOKENS [--layers L] [--iters I]
 
 Each prints the mean device time per launch (CUDA events, after warm-up; the weights
 or the cache are larger than the L2 cache or rotated so that they come from HBM) and
 the bandwidth or arithmetic rate that this time means.  Sizes other than the ones
 given default to those of Mistral 7B (32 heads, 8 key/value heads, head size 128).
+
+`step` runs whole steps of the engine, kernel by kernel (no CUDA graph), on a model with
+the layer sizes of Mistral 7B, random weights and L layers: I prefill steps of
+PREFILL_TOKENS tokens, then I decode steps of BATCH sequences that hold CONTEXT tokens of
+random cache content.  It is the small case for a profiler's list of launches: which kernels
+a step consists of and how its time divides among them.
 """
 from __future__ import annotations
 
@@ -97,14 +104,67 @@ def attn_prefill(T: int, iters: int, nh=32, nkv=8, hd=128) -> None:
               f"{2.0 * nh * hd * T * T / us / 1e6:.1f} TFLOP/s (causal half counted), error word {att.take_error()}")
 
 
+MISTRAL_7B_SIZES = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral", "hidden_size": 4096,
+    "intermediate_size": 14336, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "vocab_size": 32000, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "sliding_window": 4096,
+    "max_position_embeddings": 32768, "hidden_act": "silu", "tie_word_embeddings": False,
+    "torch_dtype": "bfloat16",
+}
+
+
+def step(B: int, context: int, prefill: int, layers: int, iters: int) -> None:
+    from . import from_random
+    from .config import config_from_dict
+    from .sampling.params import SamplingParams
+    cfg = dict(MISTRAL_7B_SIZES, num_hidden_layers=layers)
+    longest = max(context + iters + 1, prefill)
+    model = from_random(config_from_dict(cfg), seed=0, dtype="bfloat16",
+                        max_tokens=B * (longest + 64) + prefill + 64, max_batch=B + 1, max_seq_len=longest + 64)
+    eng = model.engine
+    eng.use_graphs = False
+    for g in eng.cache.paged:
+        g.storage.normal_(0.0, 0.5)
+
+    def timed(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3
+
+    prompt = [[(13 * i + 1) % eng.vocab_size for i in range(prefill)]]
+    for i in range(iters):
+        (s,) = eng.start_sequences(1)
+        us = timed(lambda: eng.step([s], prompt, "last"))
+        eng.end_sequences([s])
+        print(f"prefill step {i}: {prefill} tokens, {layers} layers, {us:.0f} us")
+    slots = eng.start_sequences(B)
+    eng.cache.prepare(slots, [context] * B)
+    eng.cache.commit(slots, [context] * B)
+    toks = [[(7 * i + 3) % eng.vocab_size] for i in range(B)]
+    greedy = SamplingParams.greedy()
+    for i in range(iters):
+        us = timed(lambda: model.sampler.select(eng.step(slots, toks, "last"), greedy))
+        print(f"decode step {i}: batch {B}, context {context + i}, {layers} layers, {us:.0f} us "
+              f"(launched from Python kernel by kernel: the host's launch cost is in this time)")
+    eng.end_sequences(slots)
+    eng.check_kernels()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill"])
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "step"])
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
     a = ap.parse_args()
     if a.what == "gemm":
         gemm(*a.sizes[:4], a.iters)
+    elif a.what == "step":
+        step(a.sizes[0], a.sizes[1], a.sizes[2], a.layers, min(a.iters, 8))
     elif a.what == "attn-decode":
         attn_decode(a.sizes[0], a.sizes[1], a.iters)
     else:
