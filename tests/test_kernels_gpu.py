@@ -252,7 +252,7 @@ def test_attention_decode_bf16(nh, nkv, hd, window, use_tma):
         for b in range(B):
             assert torch.allclose(got[b], refs[b], **_attn_tol(dtype)), \
                 f"splits {n_splits} seq {b} (len {lens[b]})"
-    # whichever block merges the splits, the bits are the same every time
+    # the same bits every time
     first = None
     for _ in range(12):
         out = torch.full((B, nh * hd), float("nan"), dtype=dtype, device=DEV)

@@ -32,11 +32,6 @@
 
 __device__ int tl_attn_tma_error = 0;
 
-// Splits of a (sequence, kv head) that have left their partial result; the block that finds
-// the count complete merges them all and sets the count back to 0 for the next launch.
-#define TD_COUNTERS 16384
-__device__ unsigned int tl_attn_tma_count[TD_COUNTERS];
-
 __device__ __forceinline__ uint32_t td_smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -96,7 +91,7 @@ FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __gri
                            __nv_bfloat16* __restrict__ out,
                            const int* __restrict__ seq_len, const int* __restrict__ seq_slot,
                            const int* __restrict__ page_table, int table_stride, int nh, int nkv,
-                           int window, float scale_log2, int n_splits, int merge_here) {
+                           int window, float scale_log2, int n_splits) {
   extern __shared__ uint8_t td_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)td_smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = (uint64_t*)(smem + TD_STAGES * TD_STAGE_BYTES);
@@ -283,73 +278,6 @@ FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __gri
       dst[d] = acc;
       if (d == 0) { dst[HEAD_DIM] = m; dst[HEAD_DIM + 1] = l; }
     }
-  }
-  if (n_splits == 1 || !merge_here) return;
-  // ---- the last split of this (sequence, kv head) to get here merges all of them, in split
-  // order whichever block it is, so the result has the same bits every run
-  __shared__ int last_one;
-  __threadfence();   // this thread's partial results are visible to the other blocks
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned int* cnt = &tl_attn_tma_count[(size_t)b * nkv + kvh];
-    const bool last = atomicAdd(cnt, 1u) == (unsigned int)(n_splits - 1);
-    if (last) *cnt = 0u;
-    last_one = last ? 1 : 0;
-  }
-  __syncthreads();
-  if (!last_one) return;
-  __threadfence();
-  // The page stages are free now: factors [G][n_splits], then sums [G][n_splits] -> [G].
-  float* sm_f = (float*)smem;
-  float* sm_ls = sm_f + G * n_splits;
-  const float* base = part + ((size_t)b * nh + (size_t)kvh * G) * n_splits * PART_STRIDE;
-  for (int i = threadIdx.x; i < G * n_splits; i += TD_WARPS * 32) {
-    sm_f[i] = __ldcg(base + (size_t)i * PART_STRIDE + HEAD_DIM);        // the split's maximum
-    sm_ls[i] = __ldcg(base + (size_t)i * PART_STRIDE + HEAD_DIM + 1);   // and its sum
-  }
-  __syncthreads();
-  // a warp per head: the largest maximum, each split's factor, and the sum of the scaled sums
-  // (lanes add their own splits in order, then the lanes are added in a fixed tree)
-  float* sm_total = sm_ls + G * n_splits;   // [G]
-  for (int r = warp; r < G; r += TD_WARPS) {
-    float m = -INFINITY;
-    for (int sidx = lane; sidx < n_splits; sidx += 32) m = fmaxf(m, sm_f[r * n_splits + sidx]);
-#pragma unroll
-    for (int o2 = 16; o2 >= 1; o2 >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o2));
-    float l = 0.0f;
-    for (int sidx = lane; sidx < n_splits; sidx += 32) {
-      const float sm = sm_f[r * n_splits + sidx];
-      const float f = sm == -INFINITY ? 0.0f : exp2f(sm - m);
-      sm_f[r * n_splits + sidx] = f;
-      l += f * sm_ls[r * n_splits + sidx];
-    }
-#pragma unroll
-    for (int o2 = 16; o2 >= 1; o2 >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o2);
-    if (lane == 0) sm_total[r] = l;
-  }
-  __syncthreads();
-  // a thread takes two dimensions of one head; 256 / HEAD_DIM heads at a time
-  constexpr int T_PER_HEAD = HEAD_DIM / 2, HEADS_AT_ONCE = TD_WARPS * 32 / T_PER_HEAD;
-  const int d2 = 2 * ((int)threadIdx.x % T_PER_HEAD);
-  for (int r = (int)threadIdx.x / T_PER_HEAD; r < G; r += HEADS_AT_ONCE) {
-    const float* src = base + (size_t)r * n_splits * PART_STRIDE + d2;
-    const float* f = sm_f + r * n_splits;
-    float ax = 0.0f, ay = 0.0f;
-    int sidx = 0;
-    for (; sidx + 8 <= n_splits; sidx += 8) {
-      float2 v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float2*>(src + (size_t)(sidx + u) * PART_STRIDE));
-#pragma unroll
-      for (int u = 0; u < 8; ++u) { ax += f[sidx + u] * v[u].x; ay += f[sidx + u] * v[u].y; }
-    }
-    for (; sidx < n_splits; ++sidx) {
-      const float2 v = __ldcg(reinterpret_cast<const float2*>(src + (size_t)sidx * PART_STRIDE));
-      ax += f[sidx] * v.x; ay += f[sidx] * v.y;
-    }
-    const float l = sm_total[r];
-    *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)b * nh + kvh * G + r) * HEAD_DIM + d2) =
-        __floats2bfloat162_rn(ax / l, ay / l);
   }
 }
 
@@ -622,21 +550,16 @@ extern "C" int FN(tl_attn_decode_tma)(const void* q, const void* k_pages, const 
   }
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(n_splits, nkv, B);
-  // the merge of the splits inside the kernel saves a launch; its counters are one static
-  // array, so launches that use it must not overlap (one stream), as everywhere in this library
-  static const int merge_env = getenv("TL_ATTN_TWO_KERNELS") ? 0 : 1;
-  const int merge_here = merge_env && (long long)B * nkv <= TD_COUNTERS &&
-                         (long long)(nh / nkv) * (2 * n_splits + 1) * 4 <= (long long)TD_STAGES * TD_STAGE_BYTES ? 1 : 0;
   int st;
   if (nh / nkv > 8)
     st = tl_launch(FN(attn_decode_tma_kernel)<true>, grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
                    (const __nv_bfloat16*)q, part, (__nv_bfloat16*)out, seq_len, seq_slot, page_table,
-                   table_stride, nh, nkv, window, scale_log2, n_splits, merge_here);
+                   table_stride, nh, nkv, window, scale_log2, n_splits);
   else
     st = tl_launch(FN(attn_decode_tma_kernel)<false>, grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
                    (const __nv_bfloat16*)q, part, (__nv_bfloat16*)out, seq_len, seq_slot, page_table,
-                   table_stride, nh, nkv, window, scale_log2, n_splits, merge_here);
-  if (st || n_splits == 1 || merge_here) return st;   // the result is written already
+                   table_stride, nh, nkv, window, scale_log2, n_splits);
+  if (st || n_splits == 1) return st;   // a single split has written the result itself
   return tl_launch(FN(attn_decode_tma_combine_kernel), dim3(nh, B), dim3(HEAD_DIM), 0, stream,
                    (const float*)part, (__nv_bfloat16*)out, nh, n_splits);
 #endif
@@ -676,10 +599,6 @@ extern "C" int FN(tl_attn_prefill_tma)(const void* q, const void* k_pages, const
 extern "C" int FN(tl_attn_tma_take_error)() {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, tl_attn_tma_error, sizeof(int)) != cudaSuccess) return -1;
-  if (v) {
-    cudaMemcpyToSymbol(tl_attn_tma_error, &zero, sizeof(int));
-    static const unsigned int zeros[TD_COUNTERS] = {};
-    cudaMemcpyToSymbol(tl_attn_tma_count, zeros, sizeof(zeros));
-  }
+  if (v) cudaMemcpyToSymbol(tl_attn_tma_error, &zero, sizeof(int));
   return v;
 }
