@@ -3,8 +3,7 @@ returns False for a case it does not take; the caller then uses the CUDA-core
 kernel."""
 from __future__ import annotations
 
-import ctypes
-from ctypes import c_float, c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong
 from typing import Dict
 
 import torch

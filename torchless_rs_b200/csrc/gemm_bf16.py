@@ -3,7 +3,7 @@ returns False for a shape it does not take; the caller then uses the CUDA-core k
 from __future__ import annotations
 
 import ctypes
-from ctypes import byref, c_float, c_int, c_longlong, c_void_p
+from ctypes import byref, c_float, c_int, c_void_p
 
 import torch
 

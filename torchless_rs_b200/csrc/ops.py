@@ -6,7 +6,6 @@ a CUDA device, a missing library or a launch that the driver rejects raises
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_void_p
 from typing import Callable, Dict, Optional
 

@@ -1,7 +1,7 @@
 """Error types of the weights layer."""
 from __future__ import annotations
 
-from typing import Dict, List, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 
 class SafetensorsFormatError(ValueError):

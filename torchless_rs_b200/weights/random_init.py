@@ -11,7 +11,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Dict, Iterator, Mapping, Tuple
+from typing import Iterator, Mapping, Tuple
 
 import torch
 
