@@ -1,11 +1,10 @@
 """Configuration and registry (no device needed)."""
 import json
-import os
 
 import pytest
 
 from tiny import CONFIGS, TINY_A, TINY_B
-from torchless_rs_b200.config import (ConfigError, LayerSpec, MistralConfig, ModelSpec, PartSpec,
+from torchless_rs_b200.config import (ConfigError, LayerSpec, MistralConfig, ModelSpec,
                                       UnknownArchitectureError, architecture_names,
                                       config_from_dict, load_config, register_architecture)
 

@@ -3,10 +3,9 @@ work: whole prompts, the last 32 tokens one by one, batches of unequal lengths w
 shorter requests end earlier, one batch after another so that slots are used again."""
 import numpy as np
 import pytest
-import torch
 
 from helpers_gpu import TinyModel, assert_close
-from tiny import CONFIGS, random_tokens
+from tiny import random_tokens
 
 pytestmark = pytest.mark.gpu
 

@@ -1,6 +1,5 @@
 """Generation through the Python entry point and the command line, the replay
 program as a user runs it, and the sampling kernels."""
-import json
 import os
 import subprocess
 import sys
@@ -9,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers_gpu import TinyModel, assert_close
+from helpers_gpu import TinyModel
 from plain import mistral_plain as plain
 from tiny import CONFIGS, make_model_dir, random_tokens, read_weights_numpy
 

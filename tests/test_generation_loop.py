@@ -3,7 +3,7 @@ needed): batches cut to fit, unequal prompts started together, stop tokens, sequ
 that end earlier and give their slot back, slots used again by the next batch."""
 import pytest
 
-from torchless_rs_b200.engine.generate import GenerationResult, generate, plan_batches
+from torchless_rs_b200.engine.generate import generate, plan_batches
 from torchless_rs_b200.sampling.params import SamplingParams, uniform_for
 
 

@@ -2,7 +2,6 @@
 than the engine tests use."""
 import math
 
-import numpy as np
 import pytest
 import torch
 

@@ -2,7 +2,6 @@
 (a layer named twice, a layer that reads another layer's cache); and a toy mixer with
 state of its own, defined here, registered, built and stepped without a change to the
 package's files."""
-import math
 
 import numpy as np
 import pytest

@@ -1,7 +1,6 @@
 """The plain implementation checked against itself and against hand-made cases (no
 device needed): it is the oracle of the GPU tests, so its parts are pinned here."""
 import numpy as np
-import pytest
 
 from plain import mistral_plain as plain
 from tiny import CONFIGS, make_model_dir, read_weights_numpy

@@ -5,7 +5,6 @@ implementation, in 32-bit and in bfloat16."""
 import json
 import os
 import subprocess
-import sys
 import tempfile
 
 import numpy as np
