@@ -1,4 +1,8 @@
-"""Free lists with ownership checks, for cache pages and for sequence slots."""
+"""Free lists with ownership checks, for cache pages and for sequence slots.
+
+The reference keeps one tensor [layers, kv heads, max_seq_len, head_dim] for the keys and one for the
+values of its single sequence (src/model/kv_cache.rs:23-53); pages and slots take its place for
+batches of sequences that come and go."""
 from __future__ import annotations
 
 from typing import List

@@ -1,4 +1,6 @@
 // Decode attention of the bfloat16 path with the cache pages brought in by TMA.
+// (Reference: per head, scores of the cached keys times 1/sqrt(head_dim), softmax with the
+// maximum subtracted, weighted sum of the cached values: src/model/modules/attention.rs:186-226.)
 //
 // Same arithmetic and the same partial results as attention_decode_bf16.cu (and the same
 // second kernel merges the splits), but keys and values do not pass through registers on

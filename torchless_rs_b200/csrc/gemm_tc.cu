@@ -2,6 +2,10 @@
 //
 //   C[M, N] (op)= X[M, K] * W[N, K]^T      X, W bfloat16 with K contiguous, 32-bit sums
 //
+// (The reference computes one output at a time as a sequential 32-bit dot product of a weight row
+// with one token's activations, widening bfloat16 on the fly: src/loader/weight_matrix.rs:82-91,
+// src/loader/parameters.rs:551-594.)
+//
 // The product is computed transposed: 128 rows of W are the M operand of tcgen05.mma,
 // a tile of BN rows of X (tokens) is its N operand, and the accumulator lies in tensor
 // memory as [128 weight rows][BN tokens].  So the same kernel serves one decoded token

@@ -1,4 +1,8 @@
-"""Token selection on the device (kernels in csrc/sampling.cu)."""
+"""Token selection on the device (kernels in csrc/sampling.cu).
+
+The reference selects on the host, one sequence at a time: arg-max, or temperature, top-k,
+softmax, top-p and an inverse-CDF draw in that order (src/sampler/mod.rs:17-238).  Here every row
+of a batch has its own parameters and its own uniform number."""
 from __future__ import annotations
 
 from typing import Optional, Sequence
