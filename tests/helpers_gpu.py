@@ -33,10 +33,14 @@ def assert_close(got: np.ndarray, ref: np.ndarray, dtype: str, what: str = "") -
 
 class TinyModel:
     def __init__(self, cfg_name: str, dtype: str, seed: int = 0, max_tokens: int = 1024,
-                 max_batch=None, store=torch.bfloat16, cfg=None):
+                 max_batch=None, store=None, cfg=None):
+        """`store`: the type the folder's tensors are written in; by default 32-bit for a
+        model that runs in 32-bit (so that products see full mantissas) and bfloat16 else."""
         import torchless_rs_b200 as tl
         self.cfg = dict(cfg if cfg is not None else CONFIGS[cfg_name])
         self.dtype = dtype
+        if store is None:
+            store = torch.float32 if dtype == "float32" else torch.bfloat16
         self.dir = make_model_dir(self.cfg, seed, store)
         self.weights = read_weights_numpy(self.dir)
         self.model = tl.load(self.dir, dtype=dtype, max_tokens=max_tokens, max_batch=max_batch)

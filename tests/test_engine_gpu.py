@@ -10,7 +10,7 @@ from tiny import random_tokens
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "C", "D", "E"]
+NAMES = ["A", "B", "C", "D", "E", "F"]
 
 
 @pytest.fixture(scope="module", params=[(n, d) for n in NAMES for d in DTYPES],
@@ -107,3 +107,61 @@ def test_long_decode(tiny):
     tiny.engine.cache.check()
     tiny.engine.end_sequences([s])
     assert_close(np.concatenate(got), ref, tiny.dtype, "long decode")
+
+
+def test_mixed_step_decode_rows_fresh_prompt_and_chunk(tiny):
+    """One step that holds a sequence going on by one token, a sequence going on by a chunk
+    of 130 tokens (on a slot that already holds 20) and a sequence that starts."""
+    x, y, z = _requests(tiny, [72, 151, 38], 21)
+    sx, sy, sz = tiny.engine.start_sequences(3)
+    got = {0: [], 1: [], 2: []}
+    out = tiny.step_np([sx, sy], [x[:70], y[:20]], "all")
+    got[0].append(out[:70]); got[1].append(out[70:])
+    out = tiny.step_np([sx, sy, sz], [[x[70]], y[20:150], z[:37]], "all")
+    got[0].append(out[:1]); got[1].append(out[1:131]); got[2].append(out[131:])
+    out = tiny.step_np([sz, sx, sy], [[z[37]], [x[71]], [y[150]]], "last")   # another row order
+    got[2].append(out[0:1]); got[0].append(out[1:2]); got[1].append(out[2:3])
+    tiny.engine.cache.check()
+    tiny.engine.end_sequences([sx, sy, sz])
+    for i, r in enumerate((x, y, z)):
+        assert_close(np.concatenate(got[i]), tiny.reference(r), tiny.dtype, f"mixed step, request {i}")
+
+
+def test_prompt_in_chunks_on_a_slot_that_holds_tokens(tiny):
+    """A prompt of 300 tokens fed as 70 + 200 + 30: the second chunk brings more than 128 new
+    tokens to a slot that is not empty (with a window, pages have been given back by then)."""
+    (toks,) = _requests(tiny, [300], 22)
+    (s,) = tiny.engine.start_sequences(1)
+    got = [tiny.step_np([s], [toks[a:b]], "all") for a, b in ((0, 70), (70, 270), (270, 300))]
+    tiny.engine.cache.check()
+    tiny.engine.end_sequences([s])
+    assert_close(np.concatenate(got), tiny.reference(toks), tiny.dtype, "prompt in chunks")
+
+
+def test_decode_across_a_length_bucket(tiny):
+    """Decoding from 250 to 520 tokens: the recorded graph's key and the split of the keys
+    among blocks change at 256 and at 512."""
+    (toks,) = _requests(tiny, [520], 23)
+    ref = tiny.reference(toks)
+    (s,) = tiny.engine.start_sequences(1)
+    got = [tiny.step_np([s], [toks[:250]], "all")]
+    for t in toks[250:]:
+        got.append(tiny.step_np([s], [[t]], "last"))
+    tiny.engine.cache.check()
+    tiny.engine.end_sequences([s])
+    assert_close(np.concatenate(got), ref, tiny.dtype, "decode 250 -> 520")
+
+
+def test_float16_folder_is_widened_exactly_on_the_32_bit_path():
+    """A folder stored in float16, run in 32-bit: the engine computes with the stored values
+    (11 bits of mantissa), not with their bfloat16 roundings, which would miss the 32-bit
+    tolerance by an order of magnitude."""
+    import torch
+    tiny = TinyModel("B", "float32", seed=41, store=torch.float16)
+    assert any(v.dtype == np.float32 and np.any(v != v.astype(np.float32).view(np.uint32).__and__(0xFFFF0000).view(np.float32))
+               for v in tiny.weights.values()), "the stored values all fit bfloat16: the test shows nothing"
+    (toks,) = _requests(tiny, [60], 42)
+    (s,) = tiny.engine.start_sequences(1)
+    got = [tiny.step_np([s], [toks[:50]], "all")] + [tiny.step_np([s], [[t]], "last") for t in toks[50:]]
+    tiny.engine.end_sequences([s])
+    assert_close(np.concatenate(got), tiny.reference(toks), "float32", "float16 folder in 32-bit")

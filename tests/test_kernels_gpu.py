@@ -506,3 +506,69 @@ def test_gemm_folds_the_norm_between_two_products(M):
     assert g.run(carry.xw, w2, act, 2, scaled=carry)
     assert torch.allclose(act.double(), ref / (1 + torch.exp(-ref)) * up, rtol=3e-2, atol=3e-2)
     assert g.take_error() == 0
+
+
+@pytest.mark.parametrize("folded_norm", [False, True])
+@pytest.mark.parametrize("style", [0, 1])
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (6, 3, 64), (12, 4, 32)])
+def test_gemm_rotates_and_writes_the_cache_itself(nh, nkv, hd, style, folded_norm):
+    """The q/k/v product of a few-token step with K split: its reduction rotates q and k at
+    each token's position and writes q, the key pages and the (transposed) value pages; the
+    32-bit q/k/v tensor is not written.  Positions cross page borders, sequences lie in
+    shuffled slots and pages; with `folded_norm` the input is a prepared norm input whose
+    1/rms scale the product applies before it rotates."""
+    from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16, RopeArgs
+    from torchless_rs_b200.parts.linear import NormCarry
+    g = GemmBf16.get()
+    dtype = torch.bfloat16
+    lens, new = [66, 129, 5, 200], [3, 2, 5, 1]
+    pc = Paged(lens, nkv, hd, dtype, 40, poison=False)
+    T, K, N, eps = sum(new), 1024, (nh + 2 * nkv) * hd, 1e-5
+    w = _rand((N, K), dtype, 41, 1.0 / math.sqrt(K))
+    if folded_norm:
+        stream = _rand((T, K), torch.float32, 42, 3.0)
+        nw = 1 + 0.1 * _rand((K,), torch.float32, 43)
+        a = (stream * nw).to(dtype)
+        carry = NormCarry(a, stream.pow(2).view(T, K // 128, 128).sum(-1).contiguous(), K, eps)
+        carry.valid = True
+        rinv = 1.0 / torch.sqrt(stream.double().pow(2).mean(1, keepdim=True) + eps)
+        qkv = (a.double() @ w.double().T) * rinv
+    else:
+        a, carry = _rand((T, K), dtype, 42), None
+        qkv = a.double() @ w.double().T
+    token_seq = torch.tensor(sum([[b] * n for b, n in enumerate(new)], []), dtype=torch.int32, device=DEV)
+    pos_list = sum([list(range(L - n, L)) for L, n in zip(lens, new)], [])
+    token_pos = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
+    half = hd // 2
+    inv = (1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64),
+                           torch.arange(half, dtype=torch.float64) / half)).float().to(DEV)
+    qo = torch.zeros((T, nh * hd), dtype=dtype, device=DEV)
+    kp, vp = torch.zeros_like(pc.k_pages), torch.zeros_like(pc.v_pages)
+    out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    rope = RopeArgs(qo.data_ptr(), kp.data_ptr(), vp.data_ptr(), token_pos.data_ptr(), token_seq.data_ptr(),
+                    pc.seq_slot.data_ptr(), pc.table.data_ptr(), inv.data_ptr(), pc.table.stride(0), style,
+                    nh, nkv, hd)
+    assert g.run(a, w, out, 0, scaled=carry, rope=rope)
+    assert g.rope_applied, "the product did not take the rotation over: this path is not under test"
+    assert g.take_error() == 0
+    assert torch.isnan(out).all(), "the 32-bit q/k/v tensor was written although the product wrote q, k and v"
+    ang = torch.tensor(pos_list, dtype=torch.float64)[:, None] * inv.cpu().double()[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    x = qkv.cpu().view(T, nh + 2 * nkv, hd)
+    rot = x[:, :nh + nkv].clone()
+    if style == 0:
+        p, q_ = rot[..., :half].clone(), rot[..., half:].clone()
+        rot[..., :half], rot[..., half:] = p * c - q_ * s, p * s + q_ * c
+    else:
+        p, q_ = rot[..., 0::2].clone(), rot[..., 1::2].clone()
+        rot[..., 0::2], rot[..., 1::2] = p * c - q_ * s, p * s + q_ * c
+    tol = dict(rtol=1e-2, atol=1e-2)
+    assert torch.allclose(qo.cpu().double().view(T, nh, hd), rot[:, :nh], **tol)
+    table = pc.table.cpu()
+    for t in range(T):
+        b, pos = int(token_seq[t]), pos_list[t]
+        page = int(table[pc.slots[b], pos // PAGE])
+        assert torch.allclose(kp[page, :, pos % PAGE, :].cpu().double(), rot[t, nh:], **tol), f"key of token {t}"
+        assert torch.allclose(vp[page, :, :, pos % PAGE].cpu().double(), x[t, nh + nkv:], **tol), f"value of token {t}"
+    assert int((kp != 0).any(-1).sum()) <= T * nkv and int((vp != 0).any(-2).sum()) <= T * nkv, \
+        "something besides the tokens' own rows was written"

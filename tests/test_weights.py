@@ -42,6 +42,7 @@ def test_written_file_reads_back_with_the_safetensors_package(tmp_path):
 
 def test_storage_rule(tmp_path):
     assert storage_dtype(torch.float16) == torch.bfloat16
+    assert storage_dtype(torch.float16, torch.float32) == torch.float32   # widened exactly for the 32-bit path
     assert storage_dtype(torch.bfloat16) == torch.bfloat16
     assert storage_dtype(torch.float32) == torch.float32     # stored in 32-bit stays so
     assert storage_dtype(torch.float64) == torch.float32
@@ -53,6 +54,15 @@ def test_storage_rule(tmp_path):
     got, src = load_checked(str(tmp_path), {"a": TensorSpec((2, 3)), "b": TensorSpec((4,)),
                                             "c": TensorSpec((5,), integer=True)})
     assert (got["a"].dtype, got["b"].dtype, got["c"].dtype) == (torch.float32, torch.bfloat16, torch.int32)
+    src.close()
+    # a float16 value that bfloat16 cannot hold survives on the 32-bit path
+    fine = torch.tensor([1.0 + 2.0 ** -10] * 4, dtype=torch.float16)
+    write_safetensors(p, [("b", fine)])
+    got, src = load_checked(str(tmp_path), {"b": TensorSpec((4,))}, torch.float32)
+    assert got["b"].dtype == torch.float32 and torch.equal(got["b"], fine.float())
+    src.close()
+    got, src = load_checked(str(tmp_path), {"b": TensorSpec((4,))}, torch.bfloat16)
+    assert got["b"].dtype == torch.bfloat16 and torch.equal(got["b"], fine.to(torch.bfloat16))
     src.close()
 
 

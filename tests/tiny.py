@@ -5,7 +5,7 @@ layers 2/3, hidden 64/96, heads 4/3, key/value heads 2/1, head size 16/32,
 intermediate 176/256, vocabulary 256/384, theta 1e4/1e6, window 16/none, eps
 1e-5/1e-6; a third has a head size that is not hidden/heads and a vocabulary that
 is no multiple of 8; a fourth has a head size and window that the tensor-core
-attention kernels take."""
+attention kernels take; a sixth is wide enough for the split-K products of decode."""
 from __future__ import annotations
 
 import os
@@ -49,7 +49,25 @@ TINY_E = {   # a width and an intermediate size that are no multiples of 8, an o
     "rope_theta": 10000.0, "sliding_window": None, "rms_norm_eps": 1e-5,
     "tie_word_embeddings": False, "max_position_embeddings": 4096,
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+TINY_F = {   # wide enough that the few-token products split K: the folded norm and the rotation
+             # inside the q/k/v product run (they need K >= 385), with a vocabulary and an
+             # intermediate size that are no multiples of 128
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 512, "num_attention_heads": 8,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 1416, "vocab_size": 1000,
+    "rope_theta": 100000.0, "sliding_window": 100, "rms_norm_eps": 2e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+# The layer sizes of Mistral 7B (hidden 4096, 32 heads over 8 key/value heads of 128, intermediate
+# 14336, window 4096) with two layers and a vocabulary of 4096, so that the folder stays below 1 GB.
+REAL_SIZES = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 4096,
+    "rope_theta": 10000.0, "sliding_window": 4096, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
 
 
 def make_model_dir(cfg: dict, seed: int, dtype=torch.bfloat16, where: str | None = None) -> str:

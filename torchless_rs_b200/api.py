@@ -118,7 +118,7 @@ def load(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
     config = load_config(model_dir)
     spec = config.model_spec()
     rt = Runtime(device, parse_dtype(dtype))
-    weights, source = load_checked(model_dir, expected_tensors(spec))
+    weights, source = load_checked(model_dir, expected_tensors(spec), rt.act_dtype)
     try:
         engine = Engine(spec, weights, rt, max_tokens or _default_max_tokens(config),
                         max_batch, max_seq_len)

@@ -25,10 +25,11 @@ from typing import Dict, List, Optional, Sequence, Union
 import numpy as np
 import torch
 
+from ..csrc.build import PAGE_TOKENS
 from .pages import CacheCapacityError, CacheStateError, FreeList
 from .requests import PagedKVRequest, StateRequest
 
-PAGE = 64
+PAGE = PAGE_TOKENS   # tokens per cache page: the number the kernels were compiled with
 
 
 def pages_for(n_tokens: int) -> int:

@@ -9,7 +9,9 @@
 #ifndef HEAD_DIM
 #define HEAD_DIM 128
 #endif
-#define PAGE 64
+#define PAGE TL_PAGE
+static_assert(PAGE == 64, "the tensor-core attention kernels lay out their shared-memory slabs, TMA "
+                          "boxes and tensor-memory columns for pages of 64 tokens");
 #define GROUP 32            // keys per warp iteration
 #define NCHUNK (HEAD_DIM / 32)  // 16-byte chunks of a K row per thread
 #define NDT (HEAD_DIM / 8)      // 8-wide tiles of the head dimension

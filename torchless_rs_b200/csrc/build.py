@@ -25,7 +25,11 @@ from typing import Dict, List, Sequence, Tuple
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+# Tokens per cache page: the one definition.  The kernels get it as -DTL_PAGE, the cache and
+# the generation loop import it from here.
+PAGE_TOKENS = 64
+BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+              f"-DTL_PAGE={PAGE_TOKENS}"]
 
 # library name -> (sources, defines)
 LIBRARIES: Dict[str, Tuple[Sequence[str], Sequence[str]]] = {
@@ -43,9 +47,7 @@ class BuildError(RuntimeError):
 
 
 def register_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()) -> None:
-    # $TL_NVCC_FLAGS: extra compiler flags for experiments (they enter the library's hash)
-    extra = tuple(os.environ.get("TL_NVCC_FLAGS", "").split())
-    LIBRARIES[name] = (tuple(sources), tuple(defines) + extra)
+    LIBRARIES[name] = (tuple(sources), tuple(defines))
 
 
 def find_nvcc() -> str:

@@ -21,7 +21,7 @@ typedef __nv_bfloat16 act_t;
 #define TL_NAME(base) base##_bf16
 #endif
 
-#define TL_PAGE 64  // tokens per cache page
+#include "pdl.cuh"   // TL_PAGE, tokens per cache page, comes from the build
 
 // Launch status: 0 = ok, otherwise the cudaError_t of the launch, or a negative
 // code for arguments that a kernel refuses.

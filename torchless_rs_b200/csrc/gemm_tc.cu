@@ -34,8 +34,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
-
 #include "pdl.cuh"
 
 #include <map>
@@ -209,8 +207,8 @@ struct GemmArgs {
   // columns are query heads, then key heads, then value heads of `hd` columns each.
   int rope_on, rope_style, rope_nh, rope_nkv, rope_hd, rope_table_stride;
   __nv_bfloat16* rope_q;    // [M, nh * hd]
-  __nv_bfloat16* rope_k;    // key pages [pages, nkv, 64, hd]
-  __nv_bfloat16* rope_v;    // value pages [pages, nkv, hd, 64]
+  __nv_bfloat16* rope_k;    // key pages [pages, nkv, TL_PAGE, hd]
+  __nv_bfloat16* rope_v;    // value pages [pages, nkv, hd, TL_PAGE]
   const int* rope_pos;      // [M] position of each token
   const int* rope_seq;      // [M] batch row of each token
   const int* rope_slot;     // cache slot of each batch row
@@ -545,13 +543,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                 args.rope_q[(size_t)m_tok * args.rope_nh * hd + n] = __float2bfloat16_rn(res);
               } else {
                 const int page = args.rope_table[(size_t)args.rope_slot[args.rope_seq[m_tok]] * args.rope_table_stride +
-                                                 pos / 64];
+                                                 pos / TL_PAGE];
                 if (page >= 0) {
                   const bool is_k = head < args.rope_nh + args.rope_nkv;
                   const int kvh = head - args.rope_nh - (is_k ? 0 : args.rope_nkv);
-                  const size_t base = ((size_t)page * args.rope_nkv + kvh) * (size_t)(64 * hd);
-                  if (is_k) args.rope_k[base + (size_t)(pos % 64) * hd + d] = __float2bfloat16_rn(res);
-                  else args.rope_v[base + (size_t)d * 64 + (pos % 64)] = __float2bfloat16_rn(res);
+                  const size_t base = ((size_t)page * args.rope_nkv + kvh) * (size_t)(TL_PAGE * hd);
+                  if (is_k) args.rope_k[base + (size_t)(pos % TL_PAGE) * hd + d] = __float2bfloat16_rn(res);
+                  else args.rope_v[base + (size_t)d * TL_PAGE + (pos % TL_PAGE)] = __float2bfloat16_rn(res);
                 }
               }
             }
@@ -1169,8 +1167,7 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int 
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splits;   // the splits of one tile share their partials
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  static const int pdl_on = getenv("TL_NO_PDL") ? 0 : 1;
-  attr[1].val.programmaticStreamSerializationAllowed = pdl_on;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWIGLU>, tw, tx, a);
@@ -1201,9 +1198,8 @@ static int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, GemmA
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  static const int pdl_on = getenv("TL_NO_PDL") ? 0 : 1;
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_on;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_persistent_kernel<BN, SWIGLU>, tw, tx, a, m_tiles, total);
@@ -1229,9 +1225,8 @@ static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a,
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  static const int pdl_on = getenv("TL_NO_PDL") ? 0 : 1;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = pdl_on;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   static int max_pairs = -1;   // per instantiation
@@ -1323,7 +1318,6 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   // Many tokens: the persistent kernels with two accumulators.
   const bool persistent = M > 128 && !ss_in;
   if (persistent) bn = swiglu ? 128 : 256;
-  static const int pair_on = getenv("TL_NO_PAIR") ? 0 : 1;
   const int pairs = num_sms / 2;
   const int pair_n = swiglu ? 128 : 256;
   // token tiles of equal width, a multiple of 32 (300 tokens: two tiles of 160, not 256 + 44)
@@ -1341,7 +1335,7 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
     }
   }
   const bool use_pair = persistent;
-  if (use_pair && pair_on) {
+  if (use_pair) {
     CUtensorMap pw, px;
     if (make_map(&pw, W, (long long)N * (swiglu ? 2 : 1), K, ldw, swiglu ? 64 : 128) &&
         make_map(&px, X, M, K, ldx, pair_bn / 2)) {
@@ -1359,12 +1353,15 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
   a.mode = mode; a.kb_per_split = kb_per_split; a.stages = 0;
   a.ss_in = ss_in; a.ss_in_tiles = ss_in_tiles; a.norm_h = norm_h; a.eps_in = eps_in;
-  const bool emit = xw_out && ss_out && nw && mode == MODE_ACCUM_F32 && splits > 1 && N % 8 == 0;
+  // the fold and the rotation live in the few-token kernel's K-split reduction only: the
+  // persistent kernels neither write xw_out / ss_out nor look at the rope arguments
+  const bool emit = xw_out && ss_out && nw && mode == MODE_ACCUM_F32 && splits > 1 && !persistent &&
+                    N % 8 == 0;
   a.xw_out = emit ? (__nv_bfloat16*)xw_out : nullptr;
   a.nw = nw; a.nw_is_f32 = nw_is_f32; a.ss_out = emit ? ss_out : nullptr;
   if (emitted) *emitted = emit ? 1 : 0;
   a.rope_on = 0;
-  if (rope && mode == MODE_STORE_F32 && splits > 1) {
+  if (rope && mode == MODE_STORE_F32 && splits > 1 && !persistent) {
     const TlRopeArgs* r = (const TlRopeArgs*)rope;
     // measured: a gain for a handful of tokens, a loss from a few dozen on (every thread then
     // computes many sines and reads every partial twice)

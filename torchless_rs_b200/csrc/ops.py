@@ -18,7 +18,7 @@ MODE_ACCUM_F32 = 1
 MODE_SWIGLU = 2
 MODE_STORE_ACT = 3
 
-PAGE = 64  # tokens per cache page; the kernels are compiled with the same number
+PAGE = build.PAGE_TOKENS  # tokens per cache page; the kernels are compiled with the same number
 
 
 class KernelError(RuntimeError):
@@ -43,6 +43,7 @@ def check_kernel_errors() -> None:
         raise KernelError("a kernel ran out of a bounded wait, its results are not valid: " +
                           ", ".join(f"{n}: code {c}" for n, c in bad.items()))
 _counter = {"launches": 0}
+_by_name: Dict[str, int] = {}
 
 
 def launches() -> int:
@@ -50,10 +51,26 @@ def launches() -> int:
     return _counter["launches"]
 
 
-def add_launches(n: int) -> None:
+def launch_counts() -> Dict[str, int]:
+    """The same count by launcher ("rmsnorm", "gemm_tc", "rope_cache_write", ...): what a
+    test reads to see which kernels a step was made of."""
+    return dict(_by_name)
+
+
+def add_launches(n, sign: int = 1) -> None:
     """Counts kernels that ran without passing through this module: a replayed CUDA
-    graph launches the kernels that were counted while it was recorded."""
-    _counter["launches"] += n
+    graph launches the kernels that were counted while it was recorded.  `n` is a number or
+    a dictionary by launcher as `launch_counts` returns it."""
+    if isinstance(n, dict):
+        for k, v in n.items():
+            _by_name[k] = _by_name.get(k, 0) + sign * v
+        n = sum(n.values())
+    _counter["launches"] += sign * n
+
+
+def counts_since(before: Dict[str, int]) -> Dict[str, int]:
+    """Launches by launcher since `before` (an earlier `launch_counts()`)."""
+    return {k: v - before.get(k, 0) for k, v in _by_name.items() if v != before.get(k, 0)}
 
 
 def _stream() -> c_void_p:
@@ -70,6 +87,7 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
 
 def _check(status: int, what: str) -> None:
     _counter["launches"] += 1
+    _by_name[what] = _by_name.get(what, 0) + 1
     if status == 0:
         return
     if status == -1:

@@ -1,7 +1,12 @@
 // Launch helper and device calls for programmatic dependent launch, shared by all kernels.
 #pragma once
 #include <cuda_runtime.h>
-#include <stdlib.h>
+
+// Tokens per cache page.  The build gives the number (build.py: PAGE_TOKENS), so that the host's
+// page arithmetic and every kernel's agree by construction.
+#ifndef TL_PAGE
+#error "TL_PAGE (tokens per cache page) must be given by the build: -DTL_PAGE=<n>"
+#endif
 
 // ---------------------------------------------------------------------------
 // Programmatic dependent launch.  Every kernel of this package is launched with the
@@ -26,8 +31,7 @@ static inline int tl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  static const int pdl_on = getenv("TL_NO_PDL") ? 0 : 1;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_on;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);

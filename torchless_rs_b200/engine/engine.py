@@ -128,11 +128,11 @@ class Engine:
             self._graphs.clear()
         graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
-        before = ops.launches()
+        before = ops.launch_counts()
         with torch.cuda.graph(graph):
             logits = self.model.forward(batch)
-        recorded = ops.launches() - before    # recording launches nothing; replay runs them all
-        ops.add_launches(-recorded)
+        recorded = ops.counts_since(before)   # recording launches nothing; replay runs them all
+        ops.add_launches(recorded, -1)
         if self.rt.workspace.generation != key[3]:   # a buffer moved while recording
             return self.model.forward(batch)
         self._graphs[key] = (graph, logits, batch, recorded)

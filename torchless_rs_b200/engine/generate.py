@@ -17,9 +17,10 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
+from ..csrc.build import PAGE_TOKENS
 from ..sampling.params import SamplingParams, uniform_for
 
-PAGE = 64
+PAGE = PAGE_TOKENS
 
 
 @dataclass

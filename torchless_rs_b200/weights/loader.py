@@ -8,9 +8,13 @@ difference.  A folder holds `model.safetensors`, or
 `model.safetensors.index.json` with its shards (the reference's sharded reader
 only merges names, src/loader/formats/safetensors.rs:283-318).
 
-Storage rule: 16-bit floating tensors are kept in bfloat16, integer tensors
-become int32, and a tensor stored in 32-bit floating point stays in 32 bits.
-What a part then computes with is the part's own decision.
+Storage rule: bfloat16 tensors are kept in bfloat16, integer tensors become
+int32, and a tensor stored in 32-bit floating point stays in 32 bits.  A float16
+tensor becomes bfloat16 (rounded to nearest even) for a model that runs in
+bfloat16 and is widened exactly to 32 bits for a model that runs in 32-bit, as
+the reference widens it (src/loader/formats/safetensors.rs:374-380), so that the
+32-bit path computes with the stored values.  What a part then computes with is
+the part's own decision.
 """
 from __future__ import annotations
 
@@ -36,11 +40,14 @@ class TensorSpec:
     integer: bool = False
 
 
-def storage_dtype(stored: torch.dtype) -> torch.dtype:
+def storage_dtype(stored: torch.dtype, run_dtype: torch.dtype = torch.bfloat16) -> torch.dtype:
+    """The type a stored tensor is kept in by a model that runs in `run_dtype`."""
     if stored in (torch.float32, torch.float64):
         return torch.float32
-    if stored in (torch.float16, torch.bfloat16):
+    if stored == torch.bfloat16:
         return torch.bfloat16
+    if stored == torch.float16:
+        return torch.float32 if run_dtype == torch.float32 else torch.bfloat16
     if stored in _INTS:
         return torch.int32
     raise TypeError(f"unsupported stored dtype {stored}")
@@ -49,8 +56,9 @@ def storage_dtype(stored: torch.dtype) -> torch.dtype:
 class WeightSource:
     """Name -> tensor over the files of one model folder."""
 
-    def __init__(self, model_dir: str):
+    def __init__(self, model_dir: str, run_dtype: torch.dtype = torch.bfloat16):
         self.model_dir = model_dir
+        self.run_dtype = run_dtype
         self.files = []
         self.where: Dict[str, SafetensorsFile] = {}
         single = os.path.join(model_dir, "model.safetensors")
@@ -95,7 +103,7 @@ class WeightSource:
     def tensor(self, name: str) -> torch.Tensor:
         """The tensor in its storage dtype (see the module text), on the CPU."""
         t = self.where[name].tensor(name)
-        want = storage_dtype(t.dtype)
+        want = storage_dtype(t.dtype, self.run_dtype)
         return t if t.dtype == want else t.to(want)
 
     def close(self) -> None:
@@ -121,11 +129,12 @@ def check_against(source_name: str, have: Mapping[str, Tuple[Tuple[int, ...], to
         raise WeightsMismatchError(source_name, missing, unexpected, wrong_shape, wrong_dtype)
 
 
-def load_checked(model_dir: str, expected: Mapping[str, TensorSpec]) -> Tuple[Dict[str, torch.Tensor], WeightSource]:
-    """All expected tensors of the folder, by name, in their storage dtype, on the
-    CPU.  Tensors may view the mapped files: keep the returned source open until
-    they have been copied to the device."""
-    src = WeightSource(model_dir)
+def load_checked(model_dir: str, expected: Mapping[str, TensorSpec],
+                 run_dtype: torch.dtype = torch.bfloat16) -> Tuple[Dict[str, torch.Tensor], WeightSource]:
+    """All expected tensors of the folder, by name, in their storage dtype for a model
+    that runs in `run_dtype`, on the CPU.  Tensors may view the mapped files: keep the
+    returned source open until they have been copied to the device."""
+    src = WeightSource(model_dir, run_dtype)
     have = {n: (src.shape(n), src.stored_dtype(n)) for n in src.names()}
     check_against(model_dir, have, expected)
     return {n: src.tensor(n) for n in expected}, src
