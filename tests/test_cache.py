@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from torchless_rs_b200.cache import (PAGE, Cache, CacheCapacityError, CacheStateError, FreeList,
+from torchless_rs_b200.cache import (PAGE, Cache, CacheCapacityError, CacheRollbackError, CacheStateError, FreeList,
                                      PagedKVRequest, StateRequest)
 
 
@@ -114,3 +114,69 @@ def test_groups_by_need_and_state_is_zeroed_on_acquire():
 def test_max_tokens_rounds_up_to_pages():
     c = _cache(max_tokens=130)
     assert c.max_tokens == 192 and c.paged[0].n_pages == 3
+
+
+def test_truncate_gives_whole_pages_back_and_reset_empties_the_slot():
+    c = _cache()
+    s, other = c.acquire(2)
+    c.prepare([s, other], [300, 10])
+    c.commit([s, other], [300, 10])
+    g = c.paged[0]
+    assert g.pool.held_count == 5 + 1
+    c.truncate(s, 300)                      # nothing to do
+    c.truncate(s, 129)                      # pages 0-2 stay (129 tokens need three)
+    assert c.length(s) == 129 and g.n_cols[s] == 3 and g.pool.held_count == 3 + 1
+    assert all(int(p) == -1 for p in g.table_host[s, 3:])
+    c.check()
+    c.prepare([s], [200])                   # goes on from 129
+    c.commit([s], [200])
+    assert g.pool.held_count == 4 + 1
+    with pytest.raises(ValueError):
+        c.truncate(s, 201)
+    with pytest.raises(ValueError):
+        c.truncate(s, -1)
+    c.reset(s)
+    assert c.length(s) == 0 and g.n_cols[s] == 0 and g.pool.held_count == 1 and c.slots.is_held(s)
+    c.check()
+    c.release([s, other])
+    with pytest.raises(CacheStateError, match="not held"):
+        c.truncate(s, 0)
+    assert g.pool.held_count == 0
+    c.check()
+
+
+def test_truncate_refuses_what_a_window_has_given_back():
+    w = 100
+    c = _cache(max_tokens=4096, window=w)
+    (s,) = c.acquire(1)
+    g = c.paged[0]
+    c.prepare([s], [300])
+    c.commit([s], [300])                    # keys before 192 are gone (pages 0-2)
+    assert g.first_live[s] == 3
+    before = (g.table_host.copy(), g.pool.free_count, c.length(s))
+    with pytest.raises(CacheRollbackError, match="window"):
+        c.truncate(s, 290)                  # position 290 sees keys from 191 on: page 2 is gone
+    assert np.array_equal(before[0], g.table_host) and before[1] == g.pool.free_count and c.length(s) == before[2]
+    c.truncate(s, 291)                      # sees keys from 192 on: possible
+    assert c.length(s) == 291 and g.pool.held_count == 2
+    c.check()
+    c.reset(s)                              # always possible
+    assert g.first_live[s] == 0 and g.pool.held_count == 0
+    c.prepare([s], [70])
+    c.commit([s], [70])
+    c.check()
+
+
+def test_truncate_with_state_of_fixed_size_only_resets():
+    reqs = [PagedKVRequest(2, 16, None), StateRequest((3,))]
+    c = Cache(reqs, 512, 4, None, torch.float32, "cpu")
+    (s,) = c.acquire(1)
+    c.prepare([s], [80])
+    c.commit([s], [80])
+    c.view(1)[s] += 2.0
+    with pytest.raises(CacheRollbackError, match="state"):
+        c.truncate(s, 40)
+    assert c.length(s) == 80
+    c.reset(s)
+    assert c.length(s) == 0 and float(c.view(1)[s].abs().sum()) == 0.0 and c.paged[0].pool.held_count == 0
+    c.check()

@@ -1,10 +1,12 @@
 """Configuration and registry (no device needed)."""
 import json
 
+from dataclasses import replace
+
 import pytest
 
 from tiny import CONFIGS, TINY_A, TINY_B
-from torchless_rs_b200.config import (ConfigError, LayerSpec, MistralConfig, ModelSpec,
+from torchless_rs_b200.config import (ConfigError, LayerSpec, MistralConfig, ModelSpec, PartSpec,
                                       UnknownArchitectureError, architecture_names,
                                       config_from_dict, load_config, register_architecture)
 
@@ -117,12 +119,44 @@ def test_spec_validation_of_order_and_shared_caches():
     with_(order=[0, 1, 0]).validate()                      # a layer may run twice
     with pytest.raises(ConfigError, match="order"):
         with_(order=[0, 2]).validate()
-    shared = LayerSpec(L[1].prefix, L[1].block, L[1].mixer, L[1].feed_forward, L[1].mixer_norm,
-                       L[1].feed_forward_norm, L[1].position, cache_from=0)
+    shared = replace(L[1], cache_from=0)
     with_(layers=[L[0], shared]).validate()
     with pytest.raises(ConfigError, match="before"):
         with_(layers=[L[0], shared], order=[1, 0]).validate()
-    bad = LayerSpec(L[1].prefix, L[1].block, L[1].mixer, L[1].feed_forward, L[1].mixer_norm,
-                    L[1].feed_forward_norm, L[1].position, cache_from=5)
+    bad = replace(L[1], cache_from=5)
     with pytest.raises(ConfigError, match="does not exist"):
         with_(layers=[L[0], bad]).validate()
+    # a reader may not look further back than the owner of the cache keeps keys
+    wide = replace(L[1], cache_from=0, mixer=PartSpec("attention", {**L[1].mixer.params, "window": None}))
+    with pytest.raises(ConfigError, match="window"):
+        with_(layers=[L[0], wide]).validate()
+    narrow = replace(L[1], cache_from=0, mixer=PartSpec("attention", {**L[1].mixer.params, "window": 8}))
+    with_(layers=[L[0], narrow]).validate()
+
+
+def test_tensor_names_and_norm_roles_are_data():
+    from torchless_rs_b200.engine.model import expected_tensors
+    base = config_from_dict(TINY_A).model_spec()
+    L = list(base.layers)
+    assert L[0].tensor_prefix("mixer") == "model.layers.0.self_attn"
+    assert L[1].tensor_prefix("feed_forward_norm") == "model.layers.1.post_attention_layernorm"
+    renamed = [replace(l, prefix=f"h.{i}", names={"mixer_norm": "ln_1", "mixer": "attn",
+                                                   "feed_forward_norm": "ln_2", "feed_forward": "ffn"})
+               for i, l in enumerate(L)]
+    spec = replace(base, layers=tuple(renamed), embedding_name="wte.weight", head_name="out.weight",
+                   final_norm_prefix="ln_f")
+    names = expected_tensors(spec)
+    assert "h.1.attn.q_proj.weight" in names and "h.0.ln_2.weight" in names and "h.0.ffn.down_proj.weight" in names
+    assert "wte.weight" in names and "ln_f.weight" in names and not any(n.startswith("model.") for n in names)
+    # a layer that does not name one of its parts, or gives norms its block does not take
+    with pytest.raises(ConfigError, match="no tensor name"):
+        replace(base, layers=(replace(L[0], names={"mixer": "a", "feed_forward": "m"}), L[1])).validate()
+    with pytest.raises(ConfigError, match="takes the norms"):
+        expected_tensors(replace(base, layers=(replace(L[0], norms={"mixer_norm": L[0].norms["mixer_norm"]}), L[1])))
+    # the hooks before the first layer and after the head
+    with pytest.raises(ConfigError, match="max_positions"):
+        replace(base, position_table_name="wpe.weight").validate()
+    with pytest.raises(ConfigError, match="logit_softcap"):
+        replace(base, logit_softcap=0.0).validate()
+    table = replace(base, position_table_name="wpe.weight", max_positions=128)
+    assert expected_tensors(table)["wpe.weight"].shape == (128, base.hidden_size)

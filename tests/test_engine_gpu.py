@@ -165,3 +165,27 @@ def test_float16_folder_is_widened_exactly_on_the_32_bit_path():
     got = [tiny.step_np([s], [toks[:50]], "all")] + [tiny.step_np([s], [[t]], "last") for t in toks[50:]]
     tiny.engine.end_sequences([s])
     assert_close(np.concatenate(got), tiny.reference(toks), "float32", "float16 folder in 32-bit")
+
+
+def test_truncate_then_decode_again_gives_the_same_logits(tiny):
+    """20 tokens decoded after a prompt, the sequence rolled back to the prompt, the same 20
+    tokens decoded again: the same logits bit for bit; then rolled back to one token before
+    the prompt's end and the prompt's last token fed alone."""
+    (toks,) = _requests(tiny, [50], 31)
+    ref = tiny.reference(toks)
+    (s,) = tiny.engine.start_sequences(1)
+    tiny.step_np([s], [toks[:30]], "last")
+    first = [tiny.step_np([s], [[t]], "last") for t in toks[30:]]
+    tiny.engine.truncate(s, 30)
+    assert tiny.engine.length(s) == 30
+    tiny.engine.cache.check()
+    again = [tiny.step_np([s], [[t]], "last") for t in toks[30:]]
+    assert all(np.array_equal(a, b) for a, b in zip(first, again)), "rolled back and run again: other logits"
+    assert_close(np.concatenate(again), ref[30:], tiny.dtype, "after truncate")
+    tiny.engine.truncate(s, 29)
+    assert_close(tiny.step_np([s], [[toks[29]]], "last"), ref[29:30], tiny.dtype, "prompt's last token alone")
+    tiny.engine.reset(s)
+    assert tiny.engine.length(s) == 0
+    assert_close(tiny.step_np([s], [toks[:9]], "all"), ref[:9], tiny.dtype, "after reset")
+    tiny.engine.cache.check()
+    tiny.engine.end_sequences([s])

@@ -105,6 +105,14 @@ class Model:
     def end_sequences(self, slots) -> None:
         self.engine.end_sequences(slots)
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Rolls the sequence of `slot` back to its first `length` tokens."""
+        self.engine.truncate(slot, length)
+
+    def reset(self, slot: int) -> None:
+        """Rolls the sequence of `slot` back to empty; the slot stays held."""
+        self.engine.reset(slot)
+
 
 def _default_max_tokens(config) -> int:
     return int(getattr(config, "max_position_embeddings", 4096))

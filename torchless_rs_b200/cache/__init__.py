@@ -1,6 +1,6 @@
-from .pages import CacheCapacityError, CacheStateError, FreeList
+from .pages import CacheCapacityError, CacheRollbackError, CacheStateError, FreeList
 from .requests import PagedKVRequest, StateRequest
 from .cache import PAGE, Cache, PagedGroup, PagedView, StateGroup, pages_for
 
-__all__ = ["CacheCapacityError", "CacheStateError", "FreeList", "PagedKVRequest", "StateRequest",
+__all__ = ["CacheCapacityError", "CacheRollbackError", "CacheStateError", "FreeList", "PagedKVRequest", "StateRequest",
            "PAGE", "Cache", "PagedGroup", "PagedView", "StateGroup", "pages_for"]

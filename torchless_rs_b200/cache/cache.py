@@ -26,7 +26,7 @@ import numpy as np
 import torch
 
 from ..csrc.build import PAGE_TOKENS
-from .pages import CacheCapacityError, CacheStateError, FreeList
+from .pages import CacheCapacityError, CacheRollbackError, CacheStateError, FreeList
 from .requests import PagedKVRequest, StateRequest
 
 PAGE = PAGE_TOKENS   # tokens per cache page: the number the kernels were compiled with
@@ -97,6 +97,29 @@ class PagedGroup:
             self.table_host[slot, f:keep_from] = -1
             self.first_live[slot] = keep_from
             self._dirty.add(slot)
+
+    def can_truncate(self, slot: int, new_len: int) -> bool:
+        """Whether the keys that position `new_len` will see are still held."""
+        w = self.request.window
+        if not w or new_len == 0:
+            return True
+        return max(0, new_len - w + 1) // PAGE >= self.first_live[slot]
+
+    def truncate(self, slot: int, new_len: int) -> None:
+        """Gives back the whole pages beyond `new_len` positions.  What lies beyond `new_len`
+        in the last kept page stays there; no kernel reads past a sequence's length, and the
+        next tokens overwrite it."""
+        keep = pages_for(new_len)
+        f, c = self.first_live[slot], self.n_cols[slot]
+        if keep >= c:
+            return
+        lo = max(keep, f)
+        if c > lo:
+            self.pool.give_back(int(p) for p in self.table_host[slot, lo:c])
+        self.table_host[slot, keep:c] = -1
+        self.n_cols[slot] = keep
+        self.first_live[slot] = min(f, keep)
+        self._dirty.add(slot)
 
     def release(self, slot: int) -> None:
         f, c = self.first_live[slot], self.n_cols[slot]
@@ -217,6 +240,46 @@ class Cache:
 
     def length(self, slot: int) -> int:
         return self.lengths[slot]
+
+    def truncate(self, slot: int, length: int) -> None:
+        """Shortens the sequence of `slot` to its first `length` tokens, so that its next step
+        goes on from there.  The reference rolls its one sequence back by lowering the position
+        counter (src/main.rs:1722-1726, the chat's /retry; src/model/mod.rs:234-237 for the
+        return to zero); here whole pages beyond `length` also go back to the pool.
+
+        Raises `CacheRollbackError`, and changes nothing, if a window has already given back
+        keys that position `length` would see, or if `length` > 0 and a mixer keeps state of
+        fixed size.  `length` = 0 is always possible: pages are given back and state is zeroed."""
+        if not self.slots.is_held(slot):
+            raise CacheStateError(f"sequence slot {slot} is shortened but is not held")
+        cur = self.lengths[slot]
+        if not 0 <= length <= cur:
+            raise ValueError(f"a sequence of {cur} tokens cannot be shortened to {length}")
+        if length == cur:
+            return
+        if length > 0:
+            if self.states:
+                raise CacheRollbackError(
+                    "a mixer of this model keeps per-sequence state of fixed size, which cannot be "
+                    "rolled back; only reset (length 0) is possible")
+            for g in self.paged:
+                if not g.can_truncate(slot, length):
+                    w = g.request.window
+                    raise CacheRollbackError(
+                        f"slot {slot} cannot be shortened from {cur} to {length} tokens: position "
+                        f"{length} sees keys from {max(0, length - w + 1)} on, but the window of {w} "
+                        f"has already given back everything before {g.first_live[slot] * PAGE}")
+        for g in self.paged:
+            g.truncate(slot, length)
+            g.upload()
+        if length == 0:
+            for g in self.states:
+                g.reset(slot)
+        self.lengths[slot] = length
+
+    def reset(self, slot: int) -> None:
+        """The sequence of `slot` starts again at its first token; the slot stays held."""
+        self.truncate(slot, 0)
 
     # ---- one step ----------------------------------------------------------------
     def prepare(self, slots: Sequence[int], new_lens: Sequence[int]) -> None:

@@ -16,6 +16,12 @@ class CacheStateError(RuntimeError):
     """A slot or page was released twice or used without being held."""
 
 
+class CacheRollbackError(RuntimeError):
+    """A sequence cannot be shortened to the asked length: a window has already given back
+    keys that the shorter sequence's next position would see, or a mixer keeps state of fixed
+    size, which holds no record of earlier lengths."""
+
+
 class FreeList:
     """Integers 0..n-1 handed out lowest first; an item is either free or held,
     never both, and never lost."""

@@ -22,6 +22,11 @@ from .spec import LayerSpec, ModelSpec, PartSpec
 
 HEAD_DIM_STEP = 16
 
+# The names a Mistral layer's tensors carry under `model.layers.<i>`
+# (src/model/mod.rs:395-414, src/model/architecture.rs:114-130).
+LAYER_TENSOR_NAMES = {"mixer_norm": "input_layernorm", "mixer": "self_attn",
+                      "feed_forward_norm": "post_attention_layernorm", "feed_forward": "mlp"}
+
 
 @dataclass(frozen=True)
 class MistralConfig:
@@ -161,7 +166,8 @@ class MistralConfig:
             })
             layers.append(LayerSpec(
                 prefix=f"model.layers.{i}", block=PartSpec("prenorm"), mixer=mixer,
-                feed_forward=ffn, mixer_norm=norm, feed_forward_norm=norm, position=rope))
+                feed_forward=ffn, norms={"mixer_norm": norm, "feed_forward_norm": norm},
+                names=LAYER_TENSOR_NAMES, position=rope))
         spec = ModelSpec(
             hidden_size=self.hidden_size, vocab_size=self.vocab_size,
             embedding_name="model.embed_tokens.weight", head_name="lm_head.weight",

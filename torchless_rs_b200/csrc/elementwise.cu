@@ -4,14 +4,20 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
-// Embedding: x[t, :] = table[tokens[t], :], no scaling
-// (reference: src/model/modules/embedding.rs:15-21).
+// Embedding: x[t, :] = table[tokens[t], :]; the reference's Mistral does no more
+// (src/model/modules/embedding.rs:15-21).  Two things other arrangements put between the
+// table and the first layer are taken here, since this kernel writes the stream anyway:
+// a multiplier (`scale`, 1 = none) and a learned row per position (`pos_table`
+// [max_pos, H] with `token_pos`, null = none): x[t, :] = scale * table[tok, :] +
+// pos_table[token_pos[t], :], in 32-bit.
 // ---------------------------------------------------------------------------
 // A token may also be taken from a device buffer (the tokens that the previous step selected):
 // with `token_src` given, token t is token_src[token_from[t]] wherever token_from[t] >= 0.
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ token_from,
                              const int* __restrict__ token_src, const act_t* __restrict__ table,
-                             float* __restrict__ x, int H, int vocab) {
+                             float* __restrict__ x, int H, int vocab, float scale,
+                             const act_t* __restrict__ pos_table, const int* __restrict__ token_pos,
+                             int max_pos) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -20,15 +26,45 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // the host has checked the range already
   const act_t* src = table + (size_t)tok * H;
   float* dst = x + (size_t)t * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32(src[i]);
+  if (pos_table == nullptr) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = scale * to_f32(src[i]);
+  } else {
+    int p = token_pos[t];
+    p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);   // the host refuses longer sequences
+    const act_t* pr = pos_table + (size_t)p * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = fmaf(scale, to_f32(src[i]), to_f32(pr[i]));
+  }
 }
 
 extern "C" int TL_NAME(tl_embed)(const int* tokens, const int* token_from, const int* token_src,
-                                 const void* table, float* x, int T, int H, int vocab,
+                                 const void* table, float* x, int T, int H, int vocab, float scale,
+                                 const void* pos_table, const int* token_pos, int max_pos,
                                  cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (pos_table != nullptr && (token_pos == nullptr || max_pos <= 0)) return TL_ERR_BAD_ARG;
   return tl_launch(embed_kernel, dim3(T), dim3(256), 0, stream, tokens, token_from, token_src,
-                   (const act_t*)table, x, H, vocab);
+                   (const act_t*)table, x, H, vocab, scale, (const act_t*)pos_table, token_pos, max_pos);
+}
+
+// ---------------------------------------------------------------------------
+// Soft cap of the logits, in place: v <- cap * tanh(v / cap).  The reference's Mistral has
+// none (src/model/mod.rs:439-446); the head of another arrangement may ask for it.
+// ---------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ v, long long n, float cap) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const float inv = 1.0f / cap;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    v[i] = cap * tanhf(v[i] * inv);
+}
+
+extern "C" int TL_NAME(tl_softcap)(float* v, long long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!(cap > 0.0f)) return TL_ERR_BAD_ARG;
+  const long long blocks = (n + 255) / 256;
+  return tl_launch(softcap_kernel, dim3((unsigned)(blocks < 2368 ? blocks : 2368)), dim3(256), 0, stream, v,
+                   n, cap);
 }
 
 // ---------------------------------------------------------------------------

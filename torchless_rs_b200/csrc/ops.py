@@ -113,7 +113,7 @@ class CoreOps:
         self.act_dtype = act_dtype
         self.suffix = _SUFFIX[act_dtype]
         self.lib = build.load_library(f"core_{self.suffix}")
-        for base in ("tl_embed", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
+        for base in ("tl_embed", "tl_softcap", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
                      "tl_gemm_generic", "tl_attn_generic"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
@@ -122,9 +122,12 @@ class CoreOps:
     # x[t, :] = table[tokens[t], :]
     def embed(self, tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor,
               token_from: Optional[torch.Tensor] = None,
-              token_src: Optional[torch.Tensor] = None) -> None:
-        """With `token_src` (int32 on the device), token t is token_src[token_from[t]] wherever
-        token_from[t] >= 0, else tokens[t]."""
+              token_src: Optional[torch.Tensor] = None, scale: float = 1.0,
+              position_table: Optional[torch.Tensor] = None,
+              token_pos: Optional[torch.Tensor] = None) -> None:
+        """x[t] = scale * table[token t] (+ position_table[token_pos[t]]).  With `token_src`
+        (int32 on the device), token t is token_src[token_from[t]] wherever token_from[t] >= 0,
+        else tokens[t]."""
         _need(tokens, torch.int32, "embed tokens")
         _need(table, self.act_dtype, "embed table")
         _need(x, torch.float32, "embed out")
@@ -132,9 +135,25 @@ class CoreOps:
             _need(token_src, torch.int32, "embed token source")
             _need(token_from, torch.int32, "embed token index")
         T, H = x.shape
+        max_pos = 0
+        if position_table is not None:
+            _need(position_table, self.act_dtype, "embed position table")
+            _need(token_pos, torch.int32, "embed token positions")
+            if position_table.shape[1] != H:
+                raise KernelError("embed: the position table's width is not the stream's")
+            max_pos = position_table.shape[0]
         _check(self._tl_embed(_ptr(tokens), _ptr(token_from if token_src is not None else None),
                               _ptr(token_src), _ptr(table), _ptr(x), c_int(T), c_int(H),
-                              c_int(table.shape[0]), _stream()), "embed")
+                              c_int(table.shape[0]), c_float(scale), _ptr(position_table),
+                              _ptr(token_pos if position_table is not None else None), c_int(max_pos),
+                              _stream()), "embed")
+
+    def softcap(self, logits: torch.Tensor, cap: float) -> None:
+        """logits <- cap * tanh(logits / cap), in place."""
+        _need(logits, torch.float32, "softcap logits")
+        from ctypes import c_longlong
+        _check(self._tl_softcap(_ptr(logits), c_longlong(logits.numel()), c_float(cap), _stream()),
+               "softcap")
 
     def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
                 rows: Optional[torch.Tensor] = None) -> None:

@@ -33,6 +33,9 @@ class Engine:
         self.rt = rt
         self.model = DecoderModel(spec, rt)
         self.model.load(weights)
+        if spec.position_table_name is not None:
+            # a learned position table has a last row: no sequence may grow past it
+            max_seq_len = min(max_seq_len or spec.max_positions, spec.max_positions)
         self.cache = Cache(self.model.cache_requests(), max_tokens, max_batch, max_seq_len,
                            dtype=rt.act_dtype, device=rt.device)
         self.model.bind_cache(self.cache)
@@ -54,6 +57,17 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
+
+    def truncate(self, slot: int, length: int) -> None:
+        """Shortens a sequence to its first `length` tokens; its next step goes on from there
+        (the reference's /retry lowers its position counter the same way, src/main.rs:1722-1726).
+        Raises `CacheRollbackError` where that is not possible (see `Cache.truncate`)."""
+        self.cache.truncate(slot, length)
+
+    def reset(self, slot: int) -> None:
+        """The sequence starts again at its first token (src/model/mod.rs:234-237); the slot
+        stays held."""
+        self.cache.reset(slot)
 
     def check_kernels(self) -> None:
         """Raises if a kernel gave up on one of its bounded waits since the last check (its

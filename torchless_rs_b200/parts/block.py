@@ -12,16 +12,30 @@ from .runtime import Runtime
 
 @register_block("prenorm")
 class PreNormBlock:
-    """Interface of every block: built from its four parts, `forward(x, batch, carry=None,
-    next_norm=None)` updates the 32-bit stream `x` [tokens, hidden] in place and returns a
-    carry for `next_norm` or None."""
+    """Interface of every block: a class attribute `norm_roles` (the norms this kind of block
+    takes; a layer's spec must give exactly these), a constructor `(spec, rt, mixer,
+    feed_forward, norms)` with `norms` a dictionary by role, the attributes `mixer`,
+    `feed_forward` and `norms`, and `forward(x, batch)`, which updates the 32-bit stream `x`
+    [tokens, hidden] in place.
 
-    def __init__(self, spec, rt: Runtime, mixer, feed_forward, mixer_norm, feed_forward_norm):
+    Optional, for blocks that let the products around a norm take it over: `takes_carry =
+    True`, `first_norm` (the norm whose input the block before may prepare; None if its mixer
+    cannot use one) and `forward(x, batch, carry, next_norm)` returning a carry for
+    `next_norm` or None.  A block without `takes_carry` is called with `(x, batch)` only."""
+    norm_roles = ("mixer_norm", "feed_forward_norm")
+    takes_carry = True
+
+    def __init__(self, spec, rt: Runtime, mixer, feed_forward, norms):
         self.rt = rt
         self.mixer = mixer
         self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+        self.norms = dict(norms)
+        self.mixer_norm = norms["mixer_norm"]
+        self.feed_forward_norm = norms["feed_forward_norm"]
+
+    @property
+    def first_norm(self):
+        return self.mixer_norm if getattr(self.mixer, "accepts_carry", False) else None
 
     def forward(self, x: torch.Tensor, batch, carry=None, next_norm=None):
         """`carry`: the input of this block's first norm if the product before it prepared
