@@ -20,6 +20,9 @@ def test_options_and_positionals():
     assert o["positional"] == ["dir", "1 2 3"]
     assert cli.parse_args(["dir"])["temperature"] == 0.7      # the reference's default
     assert cli.parse_args(["--backend", "cuda", "dir"])["positional"] == ["dir"]
+    o = cli.parse_args(["--random-weights", "--weights-seed", "9", "--save-weights", "dir"])
+    assert o["random_weights"] and o["weights_seed"] == 9 and o["save_weights"] and o["positional"] == ["dir"]
+    assert not cli.parse_args(["dir"])["random_weights"]
 
 
 def test_prompts_are_token_ids():

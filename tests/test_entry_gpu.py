@@ -139,3 +139,50 @@ def test_command_line_ids_in_ids_out():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "torchless"), "--bogus", d],
                        capture_output=True, text=True, timeout=120)
     assert r.returncode == 1 and "unknown option" in r.stderr
+
+
+def test_command_line_random_weights(tmp_path):
+    """--random-weights needs config.json only; --save-weights writes the folder's tensors, and
+    a second run that reads them gives the same tokens."""
+    import json
+    import torchless_rs_b200 as tl
+    d = str(tmp_path)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(tl.config_from_dict(CONFIGS["B"]).to_dict(), f)
+    common = ["--temperature", "0", "--max-tokens", "5", "--dtype", "float32"]
+    exe = [sys.executable, os.path.join(ROOT, "bin", "torchless")]
+    r1 = subprocess.run(exe + common + ["--random-weights", "--weights-seed", "4", "--save-weights", d, "7 8 9"],
+                        capture_output=True, text=True, timeout=600)
+    assert r1.returncode == 0, r1.stderr
+    assert os.path.isfile(os.path.join(d, "model.safetensors"))
+    r2 = subprocess.run(exe + common + [d, "7 8 9"], capture_output=True, text=True, timeout=600)
+    assert r2.returncode == 0, r2.stderr
+    assert r1.stdout.split() == r2.stdout.split() and len(r1.stdout.split()) == 5
+    w = read_weights_numpy(d)
+    seq = [7, 8, 9]
+    for tok in r1.stdout.split():
+        assert int(tok) == int(np.argmax(plain.forward_logits(CONFIGS["B"], w, seq)[-1]))
+        seq.append(int(tok))
+
+
+def test_model_drawn_on_the_device_is_the_folder_written_from_the_same_seed(tmp_path):
+    """`from_random` draws weights on the device; `write_random_model` on the host writes the
+    same values from the same seed, so the plain implementation can follow a model that never
+    was a folder."""
+    import numpy as np
+    import torchless_rs_b200 as tl
+    from plain import mistral_plain as plain
+    from tiny import TINY_B, read_weights_numpy
+    cfg = tl.config_from_dict(TINY_B)
+    m = tl.from_random(cfg, seed=21, dtype="float32", max_tokens=256)
+    d = tl.write_random_model(cfg, str(tmp_path), 21, torch.float32, "cpu")
+    w = read_weights_numpy(d)
+    toks = [int(t) for t in np.random.default_rng(1).integers(0, TINY_B["vocab_size"], 25)]
+    (s,) = m.start_sequences(1)
+    got = m.step([s], [toks], "all").cpu().numpy()
+    m.end_sequences([s])
+    ref = plain.forward_logits(TINY_B, w, toks)
+    assert (np.abs(got - ref) <= 5e-5 + 1e-4 * np.abs(ref)).all()
+    m2 = tl.load(d, dtype="float32", max_tokens=256)
+    (s,) = m2.start_sequences(1)
+    assert np.array_equal(m2.step([s], [toks], "all").cpu().numpy(), got)

@@ -572,3 +572,19 @@ def test_gemm_rotates_and_writes_the_cache_itself(nh, nkv, hd, style, folded_nor
         assert torch.allclose(vp[page, :, :, pos % PAGE].cpu().double(), x[t, nh + nkv:], **tol), f"value of token {t}"
     assert int((kp != 0).any(-1).sum()) <= T * nkv and int((vp != 0).any(-2).sum()) <= T * nkv, \
         "something besides the tokens' own rows was written"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,integer", [((3, 5), False), ((1025, 1031), False), ((4097,), False),
+                                           ((70, 9), True)])
+def test_random_weights_same_bits_on_host_and_device(dtype, shape, integer):
+    """The fill kernel and the host code draw the same bits for (seed, name, index): across a
+    chunk border of the host code (1025 x 1031 > 2^20), for odd counts, vectors (norm
+    weights: 1 + N(0, 0.1)) and integer tables."""
+    from torchless_rs_b200.weights import TensorSpec, random_tensor
+    spec = TensorSpec(shape, integer=integer)
+    host = random_tensor("some.tensor.weight", spec, 12, dtype, "cpu")
+    dev = random_tensor("some.tensor.weight", spec, 12, dtype, DEV)
+    assert dev.is_cuda and dev.dtype == host.dtype and dev.shape == host.shape
+    assert torch.equal(dev.cpu(), host)
+    assert not torch.equal(host, random_tensor("some.tensor.weight", spec, 13, dtype, "cpu"))

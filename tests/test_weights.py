@@ -148,3 +148,23 @@ def test_random_weights_depend_on_seed_and_name_only(tmp_path):
     w1, w2 = read_weights_numpy(d1), read_weights_numpy(d2)
     assert all(np.array_equal(w1[k], w2[k]) for k in w1)
     assert json.load(open(os.path.join(d1, "config.json")))["sliding_window"] == 16
+
+
+def test_random_stream_is_a_function_of_key_and_index():
+    """Any stretch of a tensor can be drawn by itself; the numbers are standard normal; the
+    polynomials that stand in for ln, sin and cos agree with the library's to rounding."""
+    from torchless_rs_b200.weights.random_init import _bits, standard_normals, tensor_key
+    key = tensor_key(3, "model.layers.0.mlp.up_proj.weight")
+    whole = standard_normals(key, 0, 5000)
+    assert np.array_equal(whole[137:1500], standard_normals(key, 137, 1363))
+    assert np.array_equal(whole[4001:], standard_normals(key, 4001, 999))
+    z = standard_normals(key, 0, 400000)
+    assert abs(z.mean()) < 5e-3 and abs(z.std() - 1) < 5e-3 and abs((z ** 4).mean() - 3) < 5e-2
+    assert abs(np.corrcoef(z[0::2], z[1::2])[0, 1]) < 5e-3        # the two numbers of a pair
+    # Box-Muller with the library's functions on the same bits
+    i = np.arange(5000, dtype=np.uint64)
+    bits = _bits(key, i >> np.uint64(1))
+    u1 = ((bits >> np.uint64(32)).astype(np.float64) + 1.0) / 2.0 ** 32
+    ang = 2.0 * np.pi * (bits & np.uint64(0xFFFFFFFF)).astype(np.float64) / 2.0 ** 32
+    lib = np.sqrt(-2.0 * np.log(u1)) * np.where(i % 2 == 0, np.cos(ang), np.sin(ang))
+    assert np.allclose(whole, lib, rtol=0, atol=1e-13)

@@ -75,7 +75,9 @@ def make_model_dir(cfg: dict, seed: int, dtype=torch.bfloat16, where: str | None
     from torchless_rs_b200 import write_random_model
     from torchless_rs_b200.config import config_from_dict
     d = where or tempfile.mkdtemp(prefix="tl_model_")
-    write_random_model(config_from_dict(cfg), d, seed, dtype)
+    # drawn on the GPU where there is one (the same bits as on the host, much faster)
+    device = "cuda:0" if torch.cuda.is_available() and dtype != torch.float16 else "cpu"
+    write_random_model(config_from_dict(cfg), d, seed, dtype, device)
     return d
 
 

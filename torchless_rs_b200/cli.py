@@ -28,6 +28,11 @@ Options:
   --backend <BACKEND>   Compute backend: auto or cuda (the only one here)
   --dtype <TYPE>        bfloat16 (default) or float32 (true 32-bit everywhere)
   --seed <S>            Seed of the sampling draws (default: 0)
+  --random-weights      Draw the weights from --weights-seed instead of reading
+                        model.safetensors (<model_path> then needs config.json only)
+  --weights-seed <S>    Seed of --random-weights (default: 0)
+  --save-weights        With --random-weights: also write model.safetensors into
+                        <model_path> (the same values)
   --stop <IDS>          Comma-separated stop token ids (default: none, as the
                         reference's single-shot mode; 'config' = the model's end tokens)
   --debug               Enable debug output
@@ -84,7 +89,8 @@ class CliError(Exception):
 
 def parse_args(argv: List[str]) -> dict:
     opts = dict(max_tokens=None, max_seq_len=None, temperature=0.7, top_k=None, top_p=None,
-                dtype="bfloat16", seed=0, stop=(), debug=False, help=False, positional=[])
+                dtype="bfloat16", seed=0, stop=(), debug=False, help=False, positional=[],
+                random_weights=False, weights_seed=0, save_weights=False)
     i = 0
 
     def value(name: str, conv):
@@ -115,6 +121,12 @@ def parse_args(argv: List[str]) -> dict:
             opts["dtype"] = value(a, str)
         elif a == "--seed":
             opts["seed"] = value(a, int)
+        elif a == "--random-weights":
+            opts["random_weights"] = True
+        elif a == "--weights-seed":
+            opts["weights_seed"] = value(a, int)
+        elif a == "--save-weights":
+            opts["save_weights"] = True
         elif a == "--stop":
             v = value(a, str)
             opts["stop"] = "config" if v == "config" else tuple(int(t) for t in v.split(",") if t)
@@ -180,9 +192,21 @@ def main(argv: Optional[List[str]] = None, prog: str = "torchless") -> int:
     if opts["debug"]:
         print(f"Loading {model_dir} ({opts['dtype']}), {len(prompts)} prompt(s), "
               f"max_tokens {max_tokens}, max_seq_len {max_seq_len}", file=sys.stderr)
+    if opts["save_weights"] and not opts["random_weights"]:
+        print("Error: --save-weights goes with --random-weights", file=sys.stderr)
+        return 1
     try:
-        model = api.load(model_dir, dtype=opts["dtype"], max_tokens=per_seq * len(prompts),
-                         max_batch=len(prompts), max_seq_len=max_seq_len)
+        if opts["random_weights"]:
+            if opts["save_weights"]:
+                from .weights import write_random_model
+                write_random_model(config, model_dir, opts["weights_seed"], api.parse_dtype(opts["dtype"]),
+                                   "cuda:0")
+            model = api.from_random(config, seed=opts["weights_seed"], dtype=opts["dtype"],
+                                    max_tokens=per_seq * len(prompts), max_batch=len(prompts),
+                                    max_seq_len=max_seq_len)
+        else:
+            model = api.load(model_dir, dtype=opts["dtype"], max_tokens=per_seq * len(prompts),
+                             max_batch=len(prompts), max_seq_len=max_seq_len)
     except Exception as e:
         print(f"Error: {e}", file=sys.stderr)
         return 1

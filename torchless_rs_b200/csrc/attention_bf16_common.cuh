@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "bounded_wait.cuh"
 #include "pdl.cuh"
 
 #ifndef HEAD_DIM

@@ -29,7 +29,6 @@
 #define K_BYTES (PAGE * HEAD_DIM * 2)
 #define V_BYTES (HEAD_DIM * PAGE * 2)
 #define TD_STAGE_BYTES (K_BYTES + V_BYTES)
-#define TD_WAIT_LIMIT (1u << 22)
 #define PART_STRIDE (HEAD_DIM + 2)
 
 __device__ int tl_attn_tma_error = 0;
@@ -50,21 +49,7 @@ __device__ __forceinline__ void td_mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ bool td_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                              int code) {
-  for (uint32_t i = 0; i < TD_WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(td_smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = code;
-  atomicCAS(&tl_attn_tma_error, 0, code);
-  return false;
+  return tl_mbar_wait(bar, parity, abort_flag, code, &tl_attn_tma_error);   // bounded_wait.cuh
 }
 __device__ __forceinline__ void td_tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
                                                int y) {

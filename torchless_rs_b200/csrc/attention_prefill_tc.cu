@@ -49,7 +49,6 @@
 // from (two bfloat16 per column), and P . V takes its A operand from there: no shared memory
 // for P and no proxy fence between the softmax's stores and the tensor core's reads.
 #define TC_SMEM_BYTES (TC_Q_BYTES + TC_KSLOTS * TC_K_BYTES + TC_VSLOTS * TC_V_BYTES + 256)
-#define TC_WAIT_LIMIT (1u << 22)
 #define TC_TMEM_COLS 256   // S twice (64 columns each), then O (HEAD_DIM columns)
 
 __device__ int tl_attn_tc_error = 0;
@@ -67,21 +66,7 @@ __device__ __forceinline__ void tc_mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
-  for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(tc_smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = code;
-  atomicCAS(&tl_attn_tc_error, 0, code);
-  return false;
+  return tl_mbar_wait(bar, parity, abort_flag, code, &tl_attn_tc_error);   // bounded_wait.cuh
 }
 __device__ __forceinline__ void tc_tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
@@ -112,7 +97,7 @@ __device__ __forceinline__ void tc_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uin
 // A wait that lets the hardware park the thread (up to about a microsecond per try) instead of
 // spinning: the spinning threads would take issue slots from the softmax warps.
 __device__ __forceinline__ bool tc_mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
-  for (uint32_t i = 0; i < (TC_WAIT_LIMIT >> 2); ++i) {
+  for (uint32_t i = 0; i < (TL_WAIT_LIMIT >> 2); ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

@@ -36,6 +36,7 @@ LIBRARIES: Dict[str, Tuple[Sequence[str], Sequence[str]]] = {
     "core_f32": (("elementwise.cu", "gemm_generic.cu", "attention_generic.cu"), ("-DTL_DTYPE=0",)),
     "core_bf16": (("elementwise.cu", "gemm_generic.cu", "attention_generic.cu"), ("-DTL_DTYPE=1",)),
     "sampling": (("sampling.cu",), ()),
+    "random_init": (("random_init.cu",), ()),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -34,6 +34,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "bounded_wait.cuh"
 #include "pdl.cuh"
 
 #include <map>
@@ -44,7 +45,6 @@
 #define TILE_K 64         // K elements per shared memory tile (128 bytes)
 #define UMMA_K 16
 #define NUM_THREADS 192   // warps 0-3 epilogue, warp 4 TMA, warp 5 MMA
-#define WAIT_LIMIT (1u << 22)
 
 #define MODE_STORE_F32 0
 #define MODE_ACCUM_F32 1
@@ -56,38 +56,17 @@ __device__ int tl_gemm_tc_error = 0;
 // ---------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return tl_smem_u32(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) { tl_mbar_init(bar, count); }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when the bound is hit or another role has given up.
+// Bounded wait (bounded_wait.cuh).  Returns false when the bound is hit or another role has given up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int code) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = code;
-  atomicCAS(&tl_gemm_tc_error, 0, code);
-  return false;
+  return tl_mbar_wait(bar, parity, abort_flag, code, &tl_gemm_tc_error);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
                                             int x, int y) {
@@ -958,7 +937,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
       if (merge && ok && threadIdx.x < (unsigned)(splits - 1)) {
         // thread j waits for the partial tile of split j + 1 (same rank, two blocks further each)
         ok = false;
-        for (uint32_t i = 0; i < WAIT_LIMIT && !ok; ++i) {
+        for (uint32_t i = 0; i < TL_WAIT_LIMIT && !ok; ++i) {
           unsigned int f;
           asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
                        : "=r"(f) : "l"(&tl_pair_flag[blockIdx.x + 2 * (threadIdx.x + 1)]) : "memory");
