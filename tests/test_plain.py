@@ -1,5 +1,7 @@
 """The plain implementation checked against itself and against hand-made cases (no
 device needed): it is the oracle of the GPU tests, so its parts are pinned here."""
+import os
+
 import numpy as np
 
 from plain import mistral_plain as plain
@@ -82,3 +84,28 @@ def test_sampling_parts():
     pp = plain.sample_probs(logits, 1.0, top_p=0.5)
     assert np.isclose(pp.sum(), 1.0) and np.count_nonzero(pp) == 2
     assert plain.draw(np.array([0.2, 0.3, 0.5]), 0.25) == 1 and plain.draw(np.array([0.2, 0.3, 0.5]), 0.99) == 2
+
+
+def test_two_independent_restatements_agree(tmp_path):
+    """The numpy restatement (whole sequences, matrix products, no cache) and the C++ one
+    (one token per forward pass with a cache, sequential dot products, the reference's own
+    shape of the computation) agree to rounding on three configurations, two of them with a
+    window shorter than the sequence, from bfloat16, float16 and 32-bit folders.  The
+    reference checks one implementation against another in the same way
+    (src/model/modules/tests.rs:213-245, at 1e-4)."""
+    import subprocess
+    import torch
+    from tiny import make_model_dir, read_weights_numpy
+    src = os.path.join(os.path.dirname(__file__), "plain", "mistral_plain_onetoken.cpp")
+    exe = str(tmp_path / "mistral_plain_onetoken")
+    subprocess.run(["g++", "-O2", "-std=c++17", "-o", exe, src], check=True)
+    for name, store in (("A", torch.float32), ("B", torch.bfloat16), ("C", torch.float16)):
+        cfg = CONFIGS[name]
+        d = make_model_dir(cfg, 5, store, str(tmp_path / name))
+        toks = [int(t) for t in np.random.default_rng(1).integers(0, cfg["vocab_size"], 90)]
+        with open(os.path.join(d, "tokens.txt"), "w") as f:
+            f.write(" ".join(map(str, toks)))
+        subprocess.run([exe, d, os.path.join(d, "tokens.txt"), os.path.join(d, "logits.f32")], check=True)
+        got = np.fromfile(os.path.join(d, "logits.f32"), dtype=np.float32).reshape(len(toks), -1)
+        ref = plain.forward_logits(cfg, read_weights_numpy(d), toks)
+        assert np.abs(got - ref).max() <= 1e-5, f"configuration {name}: {np.abs(got - ref).max():.3e}"
