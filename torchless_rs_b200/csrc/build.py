@@ -39,6 +39,10 @@ LIBRARIES: Dict[str, Tuple[Sequence[str], Sequence[str]]] = {
     "random_init": (("random_init.cu",), ()),
 }
 
+# Set before any library is loaded: build the diagnostic variant whose kernels note when they
+# start and end (-DTL_TRACE; another hash, so another file).
+TRACE = False
+
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
@@ -100,9 +104,18 @@ def build_dir() -> str:
         return d
 
 
-def library_path(name: str) -> str:
+def _defines(name: str) -> Tuple[Sequence[str], Sequence[str]]:
     sources, defines = LIBRARIES[name]
-    return os.path.join(build_dir(), f"libtl_{name}_{_digest(sources, defines)}.so")
+    return sources, tuple(defines) + (("-DTL_TRACE",) if TRACE else ())
+
+
+def _file_tag(name: str) -> str:
+    return name + ("_trace" if TRACE else "")
+
+
+def library_path(name: str) -> str:
+    sources, defines = _defines(name)
+    return os.path.join(build_dir(), f"libtl_{_file_tag(name)}_{_digest(sources, defines)}.so")
 
 
 def _run_with_progress(cmd: List[str], what: str) -> None:
@@ -145,7 +158,7 @@ def build_library(name: str, verbose: bool = True, extra_flags: Sequence[str] = 
     if os.path.isfile(path):
         return path
     nvcc = find_nvcc()
-    sources, defines = LIBRARIES[name]
+    sources, defines = _defines(name)
     bdir = os.path.dirname(path)
     tag = os.path.basename(path)[:-3]
     if verbose:
@@ -165,7 +178,7 @@ def build_library(name: str, verbose: bool = True, extra_flags: Sequence[str] = 
         _run_with_progress([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs, "-lcudart"],
                            f"link {name}")
         os.replace(tmp, path)  # atomic: a concurrent builder ends with the same file
-        _remove_stale(name, path)
+        _remove_stale(_file_tag(name), path)
     finally:
         for o in objs:
             if os.path.exists(o):

@@ -18,7 +18,9 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
                              float* __restrict__ x, int H, int vocab, float scale,
                              const act_t* __restrict__ pos_table, const int* __restrict__ token_pos,
                              int max_pos) {
+  TL_TRACE_SCOPE(1, H, 1);
   pdl_wait();
+  TL_TRACE_RELEASED();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   int tok = tokens[t];
@@ -139,8 +141,10 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
 template <typename W>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                    const W* __restrict__ w, act_t* __restrict__ y, int H, float eps) {
+  TL_TRACE_SCOPE(2, H, 2);
   __shared__ float scratch[33];
   pdl_wait();
+  TL_TRACE_RELEASED();
   pdl_launch_dependents();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
@@ -394,3 +398,5 @@ extern "C" int TL_NAME(tl_silu_mul)(const float* gu, void* out, int T, int I, cu
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   return tl_launch(silu_mul_kernel, dim3(blocks), dim3(256), 0, stream, gu, (act_t*)out, I, total);
 }
+
+TL_TRACE_EXPORT(elementwise)

@@ -195,6 +195,16 @@ struct GemmArgs {
   const float* rope_inv_freq;   // [hd / 2] or null
 };
 
+// The tail of a block's shared memory, after the stages: barriers and flags (256 bytes), the
+// per-warp sums of squares of the fold (1 KB), the tokens' 1/rms (1 KB) and, for token tiles
+// of 16 without the SiLU-gate, the cosines and sines of the folded rotation (8 KB).
+#define ROPE_TABLE_HALF 64   // pairs of dimensions per token: head sizes up to 128
+#define TAIL_BYTES 2304
+#define TAIL_ROPE_BYTES (16 * ROPE_TABLE_HALF * 8)
+__device__ __forceinline__ float* tail_ssw(uint8_t* tail) { return (float*)tail + 64; }
+__device__ __forceinline__ float* tail_rinv(uint8_t* tail) { return (float*)tail + 64 + 256; }
+__device__ __forceinline__ float2* tail_cossin(uint8_t* tail) { return (float2*)(tail + TAIL_BYTES); }
+
 // 1 / sqrt(mean(x^2) + eps) of input row m from the partial sums the producer left.
 __device__ __forceinline__ float row_rinv(const GemmArgs& a, int m) {
   float ss = 0.0f;
@@ -206,6 +216,7 @@ template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                const GemmArgs args) {
+  TL_TRACE_SCOPE(3, (long long)args.N * 16 + args.mode, 8 + ((args.N >> 7) ^ (args.K >> 9) ^ args.mode));
   // A stage holds KS sub-tiles of 64 K-elements (128 bytes) per operand: two where one weight
   // matrix is read, so that the issuing thread pays its fixed cost per stage (barrier wait,
   // commit, loop: some 400 cycles) once per eight instructions; the SiLU-gate's two matrices
@@ -315,6 +326,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   } else if (warp < 4) {
     // ---- epilogue: thread = one weight row = one column of C
     pdl_wait();   // C may be read and written by earlier kernels
+    TL_TRACE_RELEASED();
+    if (splits > 1) {
+      // What the reduction after the cluster barrier needs and the product does not: done now,
+      // while the weights stream and these warps have nothing else to do.
+      const int cols = min(BN, args.M - m0);
+      if (args.ss_in) {   // 1/rms of every token: a warp per token, the partial sums spread over its lanes
+        float* rinv_c = tail_rinv(smem + (size_t)stages * STAGE_BYTES);
+        for (int c = warp; c < cols; c += 4) {
+          float ss = 0.0f;
+          for (int t = lane; t < args.ss_in_tiles; t += 32)
+            ss += __ldcg(args.ss_in + (size_t)(m0 + c) * args.ss_in_tiles + t);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (lane == 0) rinv_c[c] = 1.0f / sqrtf(ss / (float)args.norm_h + args.eps_in);
+        }
+      }
+      if (args.rope_on && args.rope_inv_freq) {   // cosine and sine of every (token, pair of dimensions)
+        float2* cs_t = tail_cossin(smem + (size_t)stages * STAGE_BYTES);
+        const int half = args.rope_hd >> 1;
+        for (int e = threadIdx.x; e < cols * half; e += 128) {
+          const int c = e / half, i = e - c * half;
+          float sn, cs;
+          sincosf((float)args.rope_pos[m0 + c] * args.rope_inv_freq[i], &sn, &cs);
+          cs_t[c * ROPE_TABLE_HALF + i] = make_float2(cs, sn);
+        }
+      }
+    }
     const bool ok = mbar_wait(acc_bar, 0, abort_flag, 3);
     tc_fence_after();
     const int row = warp * 32 + lane;
@@ -375,20 +413,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const uint32_t red_s = smem_u32(smem);
       const int cols = min(BN, args.M - m0);
       const bool live = n < args.N && !*abort_flag;
-      float* ssw = (float*)(smem + (size_t)stages * STAGE_BYTES) + 64;   // [4 warps][64] after the barriers
-      float* rinv_c = ssw + 256;                                          // [BN] scales of the input rows
-      if (args.ss_in) {   // one scale per token, all tokens at once
-        for (int c = threadIdx.x; c < cols; c += 128) rinv_c[c] = row_rinv(args, m0 + c);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
-      const int rank = (int)cluster_rank();
+      float* ssw = tail_ssw(smem + (size_t)stages * STAGE_BYTES);        // [4 warps][64] after the barriers
+      const float* rinv_c = tail_rinv(smem + (size_t)stages * STAGE_BYTES);   // [BN] scales of the input rows,
+      const float2* cs_t = tail_cossin(smem + (size_t)stages * STAGE_BYTES); // and the rotation's table: both written
+      const int rank = (int)cluster_rank();                                 // before the cluster barrier above
       const bool accum = args.mode == MODE_ACCUM_F32 && !SWIGLU;
       int my_cols = 0;
       // Without the folded rotation: a warp takes one column (token) at a time, each lane four
       // consecutive rows of it, so that partial tiles come over in 16-byte loads and C goes out
       // in 16-byte (bfloat16: 8-byte) stores; two columns per turn keep more loads in flight.
-      const bool vec4 = !args.rope_on && (args.ldc & 3) == 0 && (args.N & 3) == 0 &&
-                        ((uintptr_t)args.C & 15) == 0 && (!args.xw_out || ((uintptr_t)args.xw_out & 7) == 0);
+      // The folded rotation goes the same way: a lane's four rows are four consecutive dimensions
+      // of one head, their partners (half a head away, or the neighbour) are with another lane of
+      // the warp or in the same four, and cosine and sine come from the table made above.
+      const bool vec4 = (args.ldc & 3) == 0 && (args.N & 3) == 0 && ((uintptr_t)args.C & 15) == 0 &&
+                        (!args.xw_out || ((uintptr_t)args.xw_out & 7) == 0) &&
+                        (!args.rope_on || (((uintptr_t)args.rope_q | (uintptr_t)args.rope_k) & 7) == 0);
       if (vec4) {
         const int n4 = n0 + 4 * lane;
         const bool live4 = n4 < args.N && !*abort_flag;   // N is a multiple of 4: all four or none
@@ -435,7 +474,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             }
             const size_t idx = (size_t)(m0 + c) * args.ldc + n4;
             float sq = 0.0f;
-            if (live4) {
+            if (!SWIGLU && args.rope_on) {
+              // dimensions d .. d + 3 of head `head`; every lane takes part in the exchange
+              const int hd = args.rope_hd, half = hd >> 1;
+              const int head = n4 / hd, d = n4 - head * hd, m_tok = m0 + c;
+              const bool turns = head < args.rope_nh + args.rope_nkv && args.rope_inv_freq != nullptr;
+              float res[4] = {val[0], val[1], val[2], val[3]};
+              if (args.rope_style == 0) {
+                float other[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) other[e] = __shfl_xor_sync(0xffffffffu, val[e], hd >> 3);
+                if (turns) {
+                  const bool first = d < half;
+                  const float2* t = cs_t + c * ROPE_TABLE_HALF + (first ? d : d - half);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    res[e] = first ? val[e] * t[e].x - other[e] * t[e].y : other[e] * t[e].y + val[e] * t[e].x;
+                }
+              } else if (turns) {
+                const float2* t = cs_t + c * ROPE_TABLE_HALF + (d >> 1);
+                res[0] = val[0] * t[0].x - val[1] * t[0].y; res[1] = val[0] * t[0].y + val[1] * t[0].x;
+                res[2] = val[2] * t[1].x - val[3] * t[1].y; res[3] = val[2] * t[1].y + val[3] * t[1].x;
+              }
+              if (live4) {
+                uint2 o;
+                o.x = pack_bf16x2(res[0], res[1]);
+                o.y = pack_bf16x2(res[2], res[3]);
+                if (head < args.rope_nh) {
+                  *reinterpret_cast<uint2*>(args.rope_q + (size_t)m_tok * args.rope_nh * hd + n4) = o;
+                } else {
+                  const int pos = args.rope_pos[m_tok];
+                  const int page = args.rope_table[(size_t)args.rope_slot[args.rope_seq[m_tok]] * args.rope_table_stride +
+                                                   pos / TL_PAGE];
+                  if (page >= 0) {
+                    const bool is_k = head < args.rope_nh + args.rope_nkv;
+                    const int kvh = head - args.rope_nh - (is_k ? 0 : args.rope_nkv);
+                    const size_t base = ((size_t)page * args.rope_nkv + kvh) * (size_t)(TL_PAGE * hd);
+                    if (is_k) {
+                      *reinterpret_cast<uint2*>(args.rope_k + base + (size_t)(pos % TL_PAGE) * hd + d) = o;
+                    } else {
+#pragma unroll
+                      for (int e = 0; e < 4; ++e)
+                        args.rope_v[base + (size_t)(d + e) * TL_PAGE + (pos % TL_PAGE)] = __float2bfloat16_rn(res[e]);
+                    }
+                  }
+                }
+              }
+            } else if (live4) {
               if (SWIGLU) {
                 uint2 o;
                 o.x = pack_bf16x2(silu_f(val[0]) * up[0], silu_f(val[1]) * up[1]);
@@ -1123,11 +1208,12 @@ template <int BN, bool SWIGLU>
 static int launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a, int splits,
                   size_t smem_budget, cudaStream_t stream) {
   const size_t stage = (SWIGLU ? 1 : 2) * ((size_t)TILE_N * TILE_K * 2 * (SWIGLU ? 2 : 1) + (size_t)BN * TILE_K * 2);
-  int stages = (int)((smem_budget - 1024 - 2048) / stage);
+  const size_t tail = TAIL_BYTES + ((BN == 16 && !SWIGLU) ? TAIL_ROPE_BYTES : 0);
+  int stages = (int)((smem_budget - 1024 - tail) / stage);
   stages = stages > 8 ? 8 : stages;
   if (stages < 2) return -2;
   a.stages = stages;
-  const size_t smem = 1024 + stages * stage + 2048;
+  const size_t smem = 1024 + stages * stage + tail;
   static size_t configured = 0;   // per instantiation
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWIGLU>,
@@ -1384,3 +1470,5 @@ extern "C" int tl_gemm_tc_take_error() {
   }
   return v;
 }
+
+TL_TRACE_EXPORT(gemm_tc)

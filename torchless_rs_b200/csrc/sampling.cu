@@ -81,8 +81,10 @@ __device__ unsigned int tl_argmax_count[ARGMAX_ROWS];
 
 __global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_parts_kernel(const float* __restrict__ logits, int ld, int V, int per_block, int* __restrict__ out) {
+  TL_TRACE_SCOPE(6, V, 6);
   __shared__ unsigned long long sw[ARGMAX_THREADS / 32];
   pdl_wait();
+  TL_TRACE_RELEASED();
   pdl_launch_dependents();
   const int r = blockIdx.y;
   const float* row = logits + (size_t)r * ld;
@@ -450,3 +452,5 @@ extern "C" int tl_sample(const float* logits, int ld, int rows, int V, float tem
   return tl_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V,
                    temperature, top_k, top_p, uniform, out);
 }
+
+TL_TRACE_EXPORT(sampling)

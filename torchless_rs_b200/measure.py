@@ -4,6 +4,7 @@
     python -m torchless_rs_b200.measure attn-decode BATCH CONTEXT [--iters I]
     python -m torchless_rs_b200.measure attn-prefill TOKENS [--iters I]
     python -m torchless_rs_b200.measure step BATCH CONTEXT PREFILL_TOKENS [--layers L] [--iters I]
+    python -m torchless_rs_b200.measure timeline BATCH CONTEXT [--layers L]
 
 Each prints the mean device time per launch (CUDA events, after warm-up; the weights
 or the cache are larger than the L2 cache or rotated so that they come from HBM) and
@@ -154,15 +155,82 @@ def step(B: int, context: int, prefill: int, layers: int, iters: int) -> None:
     eng.check_kernels()
 
 
+TRACE_KINDS = {1: "embed", 2: "rmsnorm", 3: "product", 4: "attention", 5: "attention merge", 6: "argmax"}
+
+
+def timeline(B: int, context: int, layers: int) -> None:
+    """One decode step as the engine runs it (a replayed CUDA graph): when each kernel's first
+    block started and its last block ended on the GPU's nanosecond timer, and the gap or overlap
+    between neighbours.  Uses the diagnostic build of the kernels."""
+    import ctypes
+    from .csrc import build
+    build.TRACE = True
+    from . import from_random
+    from .config import config_from_dict
+    from .sampling.params import SamplingParams
+    cfg = dict(MISTRAL_7B_SIZES, num_hidden_layers=layers)
+    model = from_random(config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=B * (context + 128),
+                        max_batch=B, max_seq_len=context + 128)
+    eng = model.engine
+    for g in eng.cache.paged:
+        g.storage.normal_(0.0, 0.5)
+    slots = eng.start_sequences(B)
+    eng.cache.prepare(slots, [context] * B)
+    eng.cache.commit(slots, [context] * B)
+    toks = [[(7 * i + 3) % eng.vocab_size] for i in range(B)]
+    greedy = SamplingParams.greedy()
+    readers = [(build.load_library("core_bf16"), "elementwise"), (build.load_library("gemm_tc"), "gemm_tc"),
+               (build.load_library("attn_bf16_hd128"), "attn_tma"), (build.load_library("sampling"), "sampling")]
+
+    def take():
+        rows = []
+        for lib, name in readers:
+            buf = (ctypes.c_ulonglong * (4 * 8192))()
+            n = getattr(lib, f"tl_trace_take_{name}")(buf, 8192)
+            rows += [tuple(buf[4 * i + j] for j in range(4)) for i in range(max(n, 0))]
+        return sorted(rows, key=lambda r: r[1])
+
+    for _ in range(5):      # eager, recorded, then replayed
+        model.sampler.select(eng.step(slots, toks, "last"), greedy)
+    torch.cuda.synchronize()
+    take()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    model.sampler.select(eng.step(slots, toks, "last"), greedy)
+    e1.record()
+    torch.cuda.synchronize()
+    rows = take()
+    t0 = rows[0][1]
+    print(f"decode step, batch {B}, context {context + 5}, {layers} layers: {e0.elapsed_time(e1) * 1e3:.1f} us by events, "
+          f"{(max(r[3] for r in rows) - t0) / 1e3:.1f} us from the first kernel's start to the last one's end")
+    print("kernel | first block starts us | let go by the kernels before us | last block ends us | "
+          "from let go to end us | from the end of the one before to this end us")
+    prev_end = None
+    for word, start, rel, end in rows:
+        kind, extra = word % 256, word // 256
+        name = TRACE_KINDS.get(kind, str(kind))
+        if kind == 3:
+            name += f" N={extra // 16} mode={extra % 16}"
+        elif kind in (4, 5):
+            name += f" splits={extra}"
+        step_ = "" if prev_end is None else f"{(end - prev_end) / 1e3:.2f}"
+        print(f"{name} | {(start - t0) / 1e3:.2f} | {(rel - t0) / 1e3:.2f} | {(end - t0) / 1e3:.2f} | "
+              f"{(end - rel) / 1e3:.2f} | {step_}")
+        prev_end = end
+    eng.end_sequences(slots)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "step"])
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "step", "timeline"])
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
     a = ap.parse_args()
     if a.what == "gemm":
         gemm(*a.sizes[:4], a.iters)
+    elif a.what == "timeline":
+        timeline(a.sizes[0], a.sizes[1], a.layers)
     elif a.what == "step":
         step(a.sizes[0], a.sizes[1], a.sizes[2], a.layers, min(a.iters, 8))
     elif a.what == "attn-decode":
