@@ -76,8 +76,10 @@ def _paged(B: int, ctx: int, nkv: int, hd: int):
 
 
 def attn_decode(B: int, ctx: int, iters: int, nh=32, nkv=8, hd=128) -> None:
-    from .csrc.attention_bf16 import AttentionBf16, decode_splits
+    from .csrc import attention_bf16
+    from .csrc.attention_bf16 import AttentionBf16
     from .parts.runtime import Workspace
+    decode_splits = attention_bf16.decode_splits
     att, ws = AttentionBf16.get(hd), Workspace(torch.device("cuda"))
     kp, vp, table, slot = _paged(B, ctx, nkv, hd)
     lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
@@ -217,6 +219,13 @@ def timeline(B: int, context: int, layers: int) -> None:
         print(f"{name} | {(start - t0) / 1e3:.2f} | {(rel - t0) / 1e3:.2f} | {(end - t0) / 1e3:.2f} | "
               f"{(end - rel) / 1e3:.2f} | {step_}")
         prev_end = end
+    # a layer's period: from the end of one q/k/v product to the end of the next
+    qkv_ends = [end for word, _, _, end in rows if word % 256 == 3 and (word // 256) % 16 == 0
+                and (word // 256) // 16 == (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]]
+    if len(qkv_ends) > 2:
+        periods = [(b - a) / 1e3 for a, b in zip(qkv_ends[1:-1], qkv_ends[2:])]
+        print(f"layer period (end of a q/k/v product to the end of the next): "
+              f"{sum(periods) / len(periods):.2f} us over {len(periods)} layers")
     eng.end_sequences(slots)
 
 
@@ -226,7 +235,12 @@ def main() -> None:
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
+    ap.add_argument("--splits", type=int, default=0,
+                    help="attn-decode, timeline: this many key splits instead of the engine's choice")
     a = ap.parse_args()
+    if a.splits:
+        from .csrc import attention_bf16
+        attention_bf16.decode_splits = lambda *args, **kw: a.splits
     if a.what == "gemm":
         gemm(*a.sizes[:4], a.iters)
     elif a.what == "timeline":
