@@ -220,7 +220,7 @@ def prefill_timed(model, lengths, repeats: int = 3):
         eng.end_sequences(slots)
         if r > 0:
             times.append(e0.elapsed_time(e1))
-    return statistics.median(times)
+    return statistics.median(times), times
 
 
 def generate_timed(model, lengths, new_tokens: int):
@@ -338,12 +338,12 @@ def main() -> int:
             p_tps, p_ms, _, _ = decode_device_timed(model, b, k, 3, CONTEXT)
             points[f"decode_b{b}"] = round(p_tps, 1)
             points[f"decode_b{b}_ms"] = round(p_ms, 3)
-        pre_ms = prefill_timed(model, prefill_lens, repeats=7)
+        pre_ms, pre_all = prefill_timed(model, prefill_lens, repeats=7)
     else:
         first_ms, e2e_ms = generate_timed(model, prefill_lens, new_tokens)
         e2e_tps = B / (e2e_ms / 1e3)
         points["first_token_ms"] = round(first_ms, 2)
-        pre_ms = prefill_timed(model, prefill_lens, repeats=3)
+        pre_ms, pre_all = prefill_timed(model, prefill_lens, repeats=3)
     clocks.stop()
     base = {"unavailable": "skipped"} if args.no_cpu_baseline else cpu_baseline(cfg, n_layers, context)
 
@@ -376,7 +376,7 @@ def main() -> int:
                 "d2h_bytes_per_step": 4 * B},
         "gpu_launches": launches,
         "prefill": {"value": round(pre_tokens / (pre_ms / 1e3), 1), "tokens": pre_tokens,
-                    "ms": round(pre_ms, 3), "of": "median",
+                    "ms": round(pre_ms, 3), "of": "median", "ms_each": [round(t, 2) for t in pre_all],
                     "frac": round(flops / (pre_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
                     "peak_tflops": peaks["bf16_tflops"],
                     "frac_of_sustained": (round(flops / (pre_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12), 4)

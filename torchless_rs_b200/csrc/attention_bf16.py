@@ -32,7 +32,7 @@ def decode_splits(batch_size: int, nkv: int, max_len: int, window) -> int:
     groups = (span + 31) // 32 + 1
     by_work = max(1, (groups + 3) // 4)          # at least one 32-key group per warp
     by_fill = max(1, TARGET_BLOCKS // max(1, batch_size * nkv))
-    return max(1, min(by_work, by_fill, 64))
+    return max(1, min(by_work, by_fill, 32))   # 32: the merge kernel fetches that many splits in one round of loads
 
 
 class AttentionBf16:

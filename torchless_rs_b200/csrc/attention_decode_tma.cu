@@ -460,9 +460,19 @@ FN(attn_decode_tma_combine_kernel)(const float* __restrict__ part, __nv_bfloat16
   const int warp = d >> 5, lane = d & 31;
   const float* src = part + ((size_t)b * nh + h) * n_splits * PART_STRIDE;
   if (n_splits <= COMBINE_MAX_SPLITS) {
+    // this thread's dimension of the first 32 splits: all loads at once, before anything waits for
+    // them (they do not depend on the factors)
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = j < n_splits ? src[j * PART_STRIDE + d] : 0.0f;
     // each split's maximum and sum, one thread per split (several rounds if there are more splits)
-    float m = -INFINITY;
-    for (int s = d; s < n_splits; s += HEAD_DIM) m = fmaxf(m, src[s * PART_STRIDE + HEAD_DIM]);
+    float m = -INFINITY, lsum[(COMBINE_MAX_SPLITS + HEAD_DIM - 1) / HEAD_DIM], msp[(COMBINE_MAX_SPLITS + HEAD_DIM - 1) / HEAD_DIM];
+    int cnt = 0;
+    for (int s = d; s < n_splits; s += HEAD_DIM, ++cnt) {
+      msp[cnt] = src[s * PART_STRIDE + HEAD_DIM];
+      lsum[cnt] = src[s * PART_STRIDE + HEAD_DIM + 1];
+      m = fmaxf(m, msp[cnt]);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if (lane == 0) red_s[warp] = m;
@@ -471,11 +481,11 @@ FN(attn_decode_tma_combine_kernel)(const float* __restrict__ part, __nv_bfloat16
 #pragma unroll
     for (int w = 1; w < HEAD_DIM / 32; ++w) m = fmaxf(m, red_s[w]);
     float l = 0.0f;
-    for (int s = d; s < n_splits; s += HEAD_DIM) {
-      const float sm = src[s * PART_STRIDE + HEAD_DIM];
-      const float f = sm == -INFINITY ? 0.0f : exp2f(sm - m);
+    cnt = 0;
+    for (int s = d; s < n_splits; s += HEAD_DIM, ++cnt) {
+      const float f = msp[cnt] == -INFINITY ? 0.0f : exp2f(msp[cnt] - m);
       f_s[s] = f;
-      l += f * src[s * PART_STRIDE + HEAD_DIM + 1];
+      l += f * lsum[cnt];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
@@ -485,15 +495,10 @@ FN(attn_decode_tma_combine_kernel)(const float* __restrict__ part, __nv_bfloat16
 #pragma unroll
     for (int w = 1; w < HEAD_DIM / 32; ++w) l += red_s[HEAD_DIM / 32 + w];
     float acc = 0.0f;
-    int s = 0;
-    for (; s + 8 <= n_splits; s += 8) {
-      float v[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = src[(s + j) * PART_STRIDE + d];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc += f_s[s + j] * v[j];
-    }
-    for (; s < n_splits; ++s) acc += f_s[s] * src[s * PART_STRIDE + d];
+    for (int j = 0; j < 32; ++j)
+      if (j < n_splits) acc += f_s[j] * v[j];
+    for (int s = 32; s < n_splits; ++s) acc += f_s[s] * src[s * PART_STRIDE + d];
     out[((size_t)b * nh + h) * HEAD_DIM + d] = __float2bfloat16_rn(acc / l);
     return;
   }
