@@ -159,19 +159,34 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const int* __res
 #pragma unroll
     for (int e = 0; e < 4; ++e) ss = fmaf(keep[j][e], keep[j][e], ss);
   }
+  // the weights do not depend on the sum: fetched before the block waits for it
+  float wv[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = 4 * (threadIdx.x + j * blockDim.x);
+    if (i < H) load4(w + i, wv[j]);
+  }
   ss = block_sum(ss, scratch);
   const float rms = sqrtf(ss / (float)H + eps);
+#if TL_DTYPE == 0
+  // the 32-bit path keeps the reference's order: divide, then multiply (src/kernels/mod.rs:558-568)
+#define NORM_SCALE(v) ((v) / rms)
+#else
+  // rounded to bfloat16 afterwards: one division per row and a multiplication per value
+  const float rinv = 1.0f / rms;
+#define NORM_SCALE(v) ((v) * rinv)
+#endif
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int i = 4 * (threadIdx.x + j * blockDim.x);
     if (i < H) {
-      float wv[4], o[4];
-      load4(w + i, wv);
+      float o[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = (keep[j][e] / rms) * wv[e];
+      for (int e = 0; e < 4; ++e) o[e] = NORM_SCALE(keep[j][e]) * wv[j][e];
       store4(yr + i, o);
     }
   }
+#undef NORM_SCALE
 }
 
 extern "C" int TL_NAME(tl_rmsnorm)(const float* x, const int* rows, const void* w, int w_is_f32,
@@ -313,13 +328,19 @@ rope_cache_write_vec_kernel(const float* __restrict__ qkv, int ld, act_t* __rest
   const int hpp = 32 / lph;           // heads per warp pass
   const int sub = lane / lph, i0 = (lane % lph) * 4;
   const int page = page_table[(size_t)seq_slot[token_seq[t]] * table_stride + pos / TL_PAGE];
-  const float fpos = (float)pos;
+  // cosine and sine of the token's angles: each once per block (a thread per pair of dimensions),
+  // then read by every lane that turns that pair; the full-precision sine is most of this
+  // kernel's arithmetic otherwise
+  float2* cs_s = reinterpret_cast<float2*>(vt);   // [hd / 2]; the value blocks use `vt` otherwise
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s_ = 0.0f, c_ = 1.0f;
+    if (inv_freq) sincosf((float)pos * inv_freq[i], &s_, &c_);
+    cs_s[i] = make_float2(c_, s_);
+  }
+  __syncthreads();
   float cs[4], sn[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    cs[j] = 1.0f; sn[j] = 0.0f;
-    if (inv_freq) sincosf(fpos * inv_freq[i0 + j], &sn[j], &cs[j]);
-  }
+  for (int j = 0; j < 4; ++j) { cs[j] = cs_s[i0 + j].x; sn[j] = cs_s[i0 + j].y; }
   const int rot_heads = nh + nkv;
   const int passes = (rot_heads + hpp - 1) / hpp;
   const int per_group = (passes + rot_groups - 1) / rot_groups;
