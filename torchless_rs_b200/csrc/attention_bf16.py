@@ -13,7 +13,8 @@ from .ops import KernelError, _check, _need, _ptr, _stream, register_error_word
 
 FAST_HEAD_DIMS = (32, 64, 128)
 MAX_GROUP = 16        # query heads per key/value head that one instruction's rows hold
-TARGET_BLOCKS = 296   # 148 SMs x 2 resident blocks: one full wave measured best
+TARGET_BLOCKS = 296   # two resident blocks on each of a B200's 148 SMs: one full wave measured best
+                      # (the default of `decode_splits`; the engine passes twice the device's own SM count)
 
 for _hd in FAST_HEAD_DIMS:
     build.register_library(f"attn_bf16_hd{_hd}",
@@ -26,12 +27,13 @@ for _hd in FAST_HEAD_DIMS:
                            (f"-DHEAD_DIM={_hd}",))
 
 
-def decode_splits(batch_size: int, nkv: int, max_len: int, window) -> int:
-    """How many blocks share the keys of one (sequence, kv head)."""
+def decode_splits(batch_size: int, nkv: int, max_len: int, window, target_blocks: int = TARGET_BLOCKS) -> int:
+    """How many blocks share the keys of one (sequence, kv head): enough for one wave of
+    `target_blocks` blocks, never more than there is work."""
     span = min(max_len, window) if window else max_len
     groups = (span + 31) // 32 + 1
     by_work = max(1, (groups + 3) // 4)          # at least one 32-key group per warp
-    by_fill = max(1, TARGET_BLOCKS // max(1, batch_size * nkv))
+    by_fill = max(1, target_blocks // max(1, batch_size * nkv))
     return max(1, min(by_work, by_fill, 32))   # 32: the merge kernel fetches that many splits in one round of loads
 
 
@@ -68,6 +70,16 @@ class AttentionBf16:
                 self._tma_error = getattr(self.lib, f"tl_attn_tma_take_error_hd{head_dim}")
                 self._tma_error.restype = c_int
                 register_error_word(f"attn_bf16_hd{head_dim}", self.take_error)
+
+    _targets: Dict[int, int] = {}
+
+    @classmethod
+    def _target_blocks(cls, device: torch.device) -> int:
+        """Two resident blocks per SM of the device the step runs on."""
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        if idx not in cls._targets:
+            cls._targets[idx] = 2 * torch.cuda.get_device_properties(idx).multi_processor_count
+        return cls._targets[idx]
 
     def take_error(self) -> int:
         """Nonzero if a TMA kernel gave up on a bounded wait since the last call (synchronises)."""
@@ -142,7 +154,7 @@ class AttentionBf16:
         if self.lib is None or nh // nkv > MAX_GROUP:
             return False
         if batch.is_decode:
-            n_splits = decode_splits(batch.n_seqs, nkv, batch.len_bucket, window)
+            n_splits = decode_splits(batch.n_seqs, nkv, batch.len_bucket, window, self._target_blocks(q.device))
             self.decode(q, cache_view.k_pages, cache_view.v_pages, out, batch.seq_len,
                         batch.seq_slot, cache_view.page_table, nh, nkv, window, scale, n_splits,
                         workspace)
