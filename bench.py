@@ -193,12 +193,17 @@ def decode_end_to_end(model, batch: int, steps: int, warmup: int, end_context: i
 
     def on_token(i, tok):
         if i == batch - 1:    # the host holds this step's tokens now (they were read from the device)
-            stamps.append(time.perf_counter())
+            stamps.append((time.perf_counter(), eng.h2d_bytes(),
+                           model._reader.bytes_copied if model._reader is not None else 0))
+    advanced = eng.steps_advanced_on_device
     model.generate(prompts, max_tokens=steps + warmup + 1, temperature=0.0, stop_ids=(),
                    on_token=on_token)
-    dt = stamps[-1] - stamps[warmup]
+    dt = stamps[-1][0] - stamps[warmup][0]
     n = len(stamps) - 1 - warmup
-    return batch * n / dt, 1e3 * dt / n
+    # bytes counted where they are copied: step layouts and page-table rows in, selected tokens out
+    h2d = (stamps[-1][1] - stamps[warmup][1]) / n
+    d2h = (stamps[-1][2] - stamps[warmup][2]) / n
+    return batch * n / dt, 1e3 * dt / n, h2d, d2h, eng.steps_advanced_on_device - advanced
 
 
 def prefill_timed(model, lengths, repeats: int = 3):
@@ -333,7 +338,7 @@ def main() -> int:
     t1 = clocks.mark()
     points = {}
     if default:
-        e2e_tps, e2e_ms = decode_end_to_end(model, B, args.steps, args.warmup, CONTEXT)
+        e2e_tps, e2e_ms, e2e_h2d, e2e_d2h, e2e_adv = decode_end_to_end(model, B, args.steps, args.warmup, CONTEXT)
         for b, k in ((1, min(args.steps, 32)), (64, min(args.steps, 16))):
             p_tps, p_ms, _, _ = decode_device_timed(model, b, k, 3, CONTEXT)
             points[f"decode_b{b}"] = round(p_tps, 1)
@@ -342,6 +347,7 @@ def main() -> int:
     else:
         first_ms, e2e_ms = generate_timed(model, prefill_lens, new_tokens)
         e2e_tps = B / (e2e_ms / 1e3)
+        e2e_h2d = e2e_d2h = e2e_adv = None
         points["first_token_ms"] = round(first_ms, 2)
         pre_ms, pre_all = prefill_timed(model, prefill_lens, repeats=3)
     clocks.stop()
@@ -372,8 +378,12 @@ def main() -> int:
             "l2": "inputs_exceed_l2", "peaks": peaks["source"],
         },
         "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": 4 * (7 * ((B + 3) // 4 * 4) + (B + 4) // 4 * 4),
-                "d2h_bytes_per_step": 4 * B},
+                # measured over the timed steps where the copies are made (the default run); a step
+                # of an unchanged batch copies no layout in, only page-table rows that gained a page
+                "h2d_bytes_per_step": (round(e2e_h2d, 1) if e2e_h2d is not None
+                                       else 4 * (8 * ((B + 3) // 4 * 4))),
+                "d2h_bytes_per_step": round(e2e_d2h, 1) if e2e_d2h is not None else 4 * B,
+                "steps_advanced_on_device": e2e_adv},
         "gpu_launches": launches,
         "prefill": {"value": round(pre_tokens / (pre_ms / 1e3), 1), "tokens": pre_tokens,
                     "ms": round(pre_ms, 3), "of": "median", "ms_each": [round(t, 2) for t in pre_all],

@@ -189,3 +189,36 @@ def test_truncate_then_decode_again_gives_the_same_logits(tiny):
     assert_close(tiny.step_np([s], [toks[:9]], "all"), ref[:9], tiny.dtype, "after reset")
     tiny.engine.cache.check()
     tiny.engine.end_sequences([s])
+
+
+def test_steady_decode_steps_advance_their_state_on_the_device(tiny):
+    """Two sequences that go on token by token with their tokens taken from a device buffer (as
+    the generation loop feeds the sampler's choices back): from the second such step on the
+    engine lays nothing out on the host; a kernel moves positions and lengths up by one.  70
+    steps cross a page border (and leave a window's pages behind); the logits equal the plain
+    implementation's, and a step of another shape in between falls back to the host's layout."""
+    import torch
+    a, b = _requests(tiny, [90, 80], 51)
+    sa, sb = tiny.engine.start_sequences(2)
+    out = tiny.step_np([sa, sb], [a[:10], b[:5]], "last")
+    got = {0: [out[0:1]], 1: [out[1:2]]}
+    src = torch.zeros(2, dtype=torch.int32, device="cuda:0")
+    before = tiny.engine.steps_advanced_on_device
+    for i in range(70):
+        src.copy_(torch.tensor([a[10 + i], b[5 + i]], dtype=torch.int32))
+        out = tiny.engine.step([sa, sb], None, "last", from_device=(src, [0, 1])).float().cpu().numpy().copy()
+        got[0].append(out[0:1]); got[1].append(out[1:2])
+    assert tiny.engine.steps_advanced_on_device - before == 69
+    # a step laid out on the host in between, then the device-fed steps again
+    out = tiny.step_np([sa, sb], [[a[80]], [b[75]]], "last")
+    got[0].append(out[0:1]); got[1].append(out[1:2])
+    for i in range(2):
+        src.copy_(torch.tensor([a[81 + i], b[76 + i]], dtype=torch.int32))
+        out = tiny.engine.step([sa, sb], None, "last", from_device=(src, [0, 1])).float().cpu().numpy().copy()
+        got[0].append(out[0:1]); got[1].append(out[1:2])
+    assert tiny.engine.steps_advanced_on_device - before == 70
+    tiny.engine.cache.check()
+    tiny.engine.end_sequences([sa, sb])
+    ref_a, ref_b = tiny.reference(a[:83]), tiny.reference(b[:78])
+    assert_close(np.concatenate(got[0]), ref_a[9:], tiny.dtype, "first sequence")
+    assert_close(np.concatenate(got[1]), ref_b[4:], tiny.dtype, "second sequence")

@@ -44,6 +44,7 @@ class OverlappedReader:
         self.bufs = [torch.empty(rows, dtype=torch.int32, pin_memory=True) for _ in range(3)]
         self.events = [torch.cuda.Event() for _ in range(3)]
         self.turn = 0
+        self.bytes_copied = 0   # device-to-host bytes so far
 
     def start(self, selected: torch.Tensor):
         n = selected.numel()
@@ -52,6 +53,7 @@ class OverlappedReader:
             self.bufs = [torch.empty(2 * n, dtype=torch.int32, pin_memory=True) for _ in range(3)]
         buf, ev = self.bufs[self.turn], self.events[self.turn]
         buf[:n].copy_(selected, non_blocking=True)
+        self.bytes_copied += 4 * n
         ev.record()
         return buf, n, ev
 

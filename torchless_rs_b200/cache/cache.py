@@ -61,6 +61,7 @@ class PagedGroup:
         self.first_live = [0] * max_slots   # first table column that still holds a page
         self.n_cols = [0] * max_slots       # table columns filled so far
         self._dirty: set = set()
+        self.bytes_copied = 0   # host-to-device bytes of page-table rows so far
         # rows on their way to the device are snapshots in pinned memory (several in rotation):
         # the host may change the table again before an earlier copy has run
         self._staging = None
@@ -153,6 +154,7 @@ class PagedGroup:
             for j, r in enumerate(rows[c0:c0 + chunk]):
                 stage_np[j] = self.table_host[r]
                 self.table_dev[r].copy_(stage[j], non_blocking=True)
+                self.bytes_copied += 4 * self.table_host.shape[1]
             ev = self._staging_events[self._turn] or torch.cuda.Event()
             ev.record()
             self._staging_events[self._turn] = ev

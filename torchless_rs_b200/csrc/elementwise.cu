@@ -420,4 +420,24 @@ extern "C" int TL_NAME(tl_silu_mul)(const float* gu, void* out, int T, int I, cu
   return tl_launch(silu_mul_kernel, dim3(blocks), dim3(256), 0, stream, gu, (act_t*)out, I, total);
 }
 
+// ---------------------------------------------------------------------------
+// The per-sequence state of a running batch on the device: each row's position and length go up
+// by one.  When a decode step has the same sequences in the same rows as the step before and its
+// tokens come from the device (the tokens the sampler selected), nothing that the kernels read
+// has changed but these two arrays, so the engine advances them here instead of laying the step
+// out on the host and copying it over.  (The reference's state is one counter that its caller
+// increments after each forward pass, src/model/mod.rs:93, src/main.rs:562.)
+// ---------------------------------------------------------------------------
+__global__ void advance_step_kernel(int* __restrict__ token_pos, int* __restrict__ seq_len, int n) {
+  pdl_wait();   // the step before still reads both arrays
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { token_pos[i] += 1; seq_len[i] += 1; }
+}
+
+extern "C" int TL_NAME(tl_advance_step)(int* token_pos, int* seq_len, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  return tl_launch(advance_step_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, token_pos, seq_len, n);
+}
+
 TL_TRACE_EXPORT(elementwise)

@@ -113,7 +113,7 @@ class CoreOps:
         self.act_dtype = act_dtype
         self.suffix = _SUFFIX[act_dtype]
         self.lib = build.load_library(f"core_{self.suffix}")
-        for base in ("tl_embed", "tl_softcap", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
+        for base in ("tl_embed", "tl_softcap", "tl_advance_step", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
                      "tl_gemm_generic", "tl_attn_generic"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
@@ -147,6 +147,16 @@ class CoreOps:
                               c_int(table.shape[0]), c_float(scale), _ptr(position_table),
                               _ptr(token_pos if position_table is not None else None), c_int(max_pos),
                               _stream()), "embed")
+
+    def advance_step(self, token_pos: torch.Tensor, seq_len: torch.Tensor) -> None:
+        """Every row's position and length go up by one, on the device (a decode step of the same
+        batch as the step before)."""
+        _need(token_pos, torch.int32, "advance positions")
+        _need(seq_len, torch.int32, "advance lengths")
+        if token_pos.numel() != seq_len.numel():
+            raise KernelError("advance_step: one position and one length per row are needed")
+        _check(self._tl_advance_step(_ptr(token_pos), _ptr(seq_len), c_int(seq_len.numel()), _stream()),
+               "advance_step")
 
     def softcap(self, logits: torch.Tensor, cap: float) -> None:
         """logits <- cap * tanh(logits / cap), in place."""

@@ -80,6 +80,8 @@ class BatchStager:
         self.hosts: List[torch.Tensor] = []
         self.events: List[Optional[torch.cuda.Event]] = []
         self.turn = 0
+        self.staged = 0      # steps laid out so far: the device buffer holds the last one's arrays
+        self.bytes_copied = 0   # host-to-device bytes of all step layouts so far
         self.dev: Optional[torch.Tensor] = None
 
     def _ensure(self, n: int) -> None:
@@ -101,6 +103,7 @@ class BatchStager:
             offs.append(total)
             total += (s + 3) // 4 * 4
         self._ensure(max(total, 1))
+        self.staged += 1
         self.turn = (self.turn + 1) % self.RING
         if self.events[self.turn] is not None:
             self.events[self.turn].synchronize()   # the copy that last used this buffer is done
@@ -109,6 +112,7 @@ class BatchStager:
         for f, o, s in zip(self.FIELDS, offs, sizes):
             hv[o:o + s] = arrays[f]
         self.dev[:total].copy_(host[:total], non_blocking=True)
+        self.bytes_copied += 4 * total
         ev = self.events[self.turn] or torch.cuda.Event()
         ev.record()
         self.events[self.turn] = ev

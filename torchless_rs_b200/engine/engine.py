@@ -45,6 +45,8 @@ class Engine:
         self.use_graphs = use_graphs
         self._graphs = {}      # key -> (CUDA graph, logits view)
         self._seen = set()     # keys that have run once without a graph
+        self._steady = None    # (key, staged count, batch) of the last decode step fed from the device
+        self.steps_advanced_on_device = 0
 
     # ---- sequences -------------------------------------------------------------------
     def start_sequences(self, count: int) -> List[int]:
@@ -68,6 +70,10 @@ class Engine:
         """The sequence starts again at its first token (src/model/mod.rs:234-237); the slot
         stays held."""
         self.cache.reset(slot)
+
+    def h2d_bytes(self) -> int:
+        """Host-to-device bytes that steps have copied so far: step layouts and page-table rows."""
+        return self.stager.bytes_copied + sum(g.bytes_copied for g in self.cache.paged)
 
     def check_kernels(self) -> None:
         """Raises if a kernel gave up on one of its bounded waits since the last check (its
@@ -108,16 +114,37 @@ class Engine:
         elif want == "none" or want is None:
             want = [[] for _ in counts]
         past = [self.cache.length(s) for s in slots]
+        new_lens = [p + c for p, c in zip(past, counts)]
+        # The same sequences in the same rows as the decode step before, fed from the device again:
+        # only positions and lengths differ, by one, and a kernel advances them on the device; the
+        # host lays nothing out and copies nothing but page-table rows that gained a page.
+        steady_key = None
+        if token_src is not None and all(c == 1 for c in counts) and all(w == [0] for w in want):
+            steady_key = (tuple(slots), tuple(int(i) for i in src_index), token_src.data_ptr())
+            st = self._steady
+            if st is not None and st[0] == steady_key and st[1] == self.stager.staged and \
+                    st[2].new_lens == past:
+                batch = st[2]
+                self.cache.prepare(slots, new_lens)
+                self.rt.ops.advance_step(batch.token_pos, batch.seq_len)
+                batch.past_lens, batch.new_lens = list(past), list(new_lens)
+                batch.max_len = max(new_lens)
+                batch.len_bucket = max(256, 1 << max(batch.max_len - 1, 0).bit_length())
+                batch.token_src = token_src
+                self.steps_advanced_on_device += 1
+                logits = self._forward(batch)
+                self.cache.commit(slots, new_lens)
+                return logits
         arrays = layout_step(past, counts, slots, tokens, want)
         if token_src is not None:
             arrays["token_from"] = np.asarray(src_index, dtype=np.int32)
         toks = arrays["tokens"]
         if toks.size and (toks.min() < 0 or toks.max() >= self.vocab_size):
             raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
-        new_lens = [p + c for p, c in zip(past, counts)]
         self.cache.prepare(slots, new_lens)
         batch = self.stager.stage(arrays, slots, past, is_decode=all(c == 1 for c in counts))
         batch.token_src = token_src
+        self._steady = (steady_key, self.stager.staged, batch) if steady_key is not None else None
         logits = self._forward(batch)
         self.cache.commit(slots, new_lens)
         return logits
