@@ -178,10 +178,10 @@ def forward_logits(cfg: dict, weights: dict, tokens, dtype=np.float32) -> np.nda
 # ---------------------------------------------------------------------------
 
 def greedy(logits: np.ndarray) -> int:
-    """Arg-max of the logits.  src/sampler/mod.rs:60-68.  (On an exact tie the
-    reference keeps the last maximal index; the package keeps the first.  Tests
-    use logits without ties.)"""
-    return int(np.argmax(logits))
+    """Arg-max of the logits; on an exact tie the last maximal index, as Rust's
+    `max_by` returns it.  src/sampler/mod.rs:60-68."""
+    n = len(logits)
+    return int(n - 1 - np.argmax(np.asarray(logits)[::-1]))
 
 
 def top_k_filter(scaled: np.ndarray, k: int) -> np.ndarray:

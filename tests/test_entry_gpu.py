@@ -99,9 +99,12 @@ def test_sampling_kernels_alone(V):
     s = Sampler("cuda:0")
     g = torch.Generator().manual_seed(V)
     logits = (torch.randn((6, V), generator=g) * 3).cuda()
-    logits[2, 5] = logits[2, 77] = logits[2].max() + 1      # a tie: the lowest index wins
-    assert s.select(logits, SamplingParams.greedy()).tolist() == [int(a) for a in
-                                                                  np.argmax(logits.cpu().numpy(), -1)]
+    logits[2, 5] = logits[2, 77] = logits[2].max() + 1      # a tie: the highest index wins, as in the reference
+    assert s.select(logits, SamplingParams.greedy()).tolist() == [plain.greedy(row) for row in logits.cpu().numpy()]
+    assert plain.greedy(logits[2].cpu().numpy()) == 77
+    many = (torch.randn((70, V), generator=g) * 3).cuda()      # 64 rows and more: one block per row
+    many[3, 5] = many[3, 77] = many[3].max() + 1
+    assert s.select(many, SamplingParams.greedy()).tolist() == [plain.greedy(row) for row in many.cpu().numpy()]
     ln = logits.cpu().numpy()
     for kw in (dict(temperature=0.7), dict(temperature=1.0, top_k=5), dict(temperature=1.0, top_k=1),
                dict(temperature=1.5, top_p=0.3), dict(temperature=0.9, top_k=50, top_p=0.9),

@@ -73,6 +73,7 @@ def test_window_changes_logits_only_beyond_the_window():
 def test_sampling_parts():
     logits = np.array([0.1, 2.0, -1.0, 2.0, 0.5], dtype=np.float32)
     assert plain.greedy(np.array([0.1, 2.0, -1.0, 1.9])) == 1              # sampler/tests.rs:34-50
+    assert plain.greedy(np.array([3.0, 1.0, 3.0])) == 2                    # Rust's max_by keeps the last of equal maxima
     f = plain.top_k_filter(logits.astype(np.float64), 1)
     assert np.isfinite(f).sum() == 1 and np.isfinite(f[1])                  # ties: first in index order
     p = plain.sample_probs(logits, 0.7)

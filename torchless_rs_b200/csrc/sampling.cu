@@ -8,8 +8,8 @@
 // sequential pass in index order.  The uniform number of each row comes from the
 // host, which derives it from (seed, sequence, step).
 //
-// Ties: arg-max keeps the lowest index (the reference's max_by keeps the last,
-// src/sampler/mod.rs:60-68); at a top-k or top-p threshold the tied entries of lowest
+// Ties: arg-max keeps the highest index among equal maxima, as the reference's max_by does
+// (src/sampler/mod.rs:60-68); at a top-k or top-p threshold the tied entries of lowest
 // index are kept (top-k: as the reference, :108-117; top-p: the reference's unstable
 // sort leaves it open, :147).
 #include <cuda_runtime.h>
@@ -40,16 +40,16 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
   pdl_launch_dependents();
   const float* row = logits + (size_t)blockIdx.x * ld;
   uint32_t best = 0u;
-  int best_i = 0x7fffffff;
+  int best_i = -1;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     const uint32_t k = float_key(row[i]);
-    if (k > best || (k == best && i < best_i)) { best = k; best_i = i; }
+    if (k > best || (k == best && i > best_i)) { best = k; best_i = i; }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const uint32_t ok = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (ok > best || (ok == best && oi < best_i)) { best = ok; best_i = oi; }
+    if (ok > best || (ok == best && oi > best_i)) { best = ok; best_i = oi; }
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) { sk[warp] = best; si[warp] = best_i; }
@@ -57,21 +57,21 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
   if (warp == 0) {
     const int nw = (blockDim.x + 31) >> 5;
     best = lane < nw ? sk[lane] : 0u;
-    best_i = lane < nw ? si[lane] : 0x7fffffff;
+    best_i = lane < nw ? si[lane] : -1;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const uint32_t ok = __shfl_xor_sync(0xffffffffu, best, o);
       const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-      if (ok > best || (ok == best && oi < best_i)) { best = ok; best_i = oi; }
+      if (ok > best || (ok == best && oi > best_i)) { best = ok; best_i = oi; }
     }
-    if (lane == 0) out[blockIdx.x] = best_i < V ? best_i : 0;
+    if (lane == 0) out[blockIdx.x] = (best_i >= 0 && best_i < V) ? best_i : 0;
   }
 }
 
 // The same with several blocks per row, for the few rows of a decode step (one block per row
 // leaves most SMs idle and takes as long as its one chain of loads).  A block folds its part
-// of the row into one 64-bit word per row with atomicMax: key in the high half, the
-// complemented index in the low half, so that among equal keys the lowest index wins.  The
+// of the row into one 64-bit word per row with atomicMax: key in the high half, the index
+// plus one in the low half, so that among equal keys the highest index wins.  The
 // block that finishes a row last writes the result and clears the row's word and counter for
 // the next launch (they are static: launches on one stream at a time).
 #define ARGMAX_ROWS 4096
@@ -92,7 +92,7 @@ argmax_parts_kernel(const float* __restrict__ logits, int ld, int V, int per_blo
   unsigned long long best = 0ull;
 #pragma unroll 4
   for (int i = begin + threadIdx.x; i < end; i += ARGMAX_THREADS) {
-    const unsigned long long w = ((unsigned long long)float_key(row[i]) << 32) | (uint32_t)~(uint32_t)i;
+    const unsigned long long w = ((unsigned long long)float_key(row[i]) << 32) | (uint32_t)(i + 1);
     best = w > best ? w : best;
   }
 #pragma unroll
@@ -109,8 +109,8 @@ argmax_parts_kernel(const float* __restrict__ logits, int ld, int V, int per_blo
     if (atomicAdd(&tl_argmax_count[r], 1u) == gridDim.x - 1) {   // every part of the row is in
       __threadfence();
       const unsigned long long w = atomicExch(&tl_argmax_word[r], 0ull);
-      const uint32_t idx = ~(uint32_t)(w & 0xffffffffull);
-      out[r] = (w != 0ull && idx < (uint32_t)V) ? (int)idx : 0;
+      const uint32_t low = (uint32_t)(w & 0xffffffffull);   // index + 1; 0: nothing was folded in
+      out[r] = (low != 0u && low <= (uint32_t)V) ? (int)(low - 1u) : 0;
       tl_argmax_count[r] = 0u;
     }
   }
