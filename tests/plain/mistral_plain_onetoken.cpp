@@ -3,8 +3,8 @@
 // no cache, this one runs the way rglonek/torchless-rs runs: one token of one sequence per
 // forward pass, keys and values kept in a cache [layer][kv head][position][head_dim], every
 // output a sequential 32-bit dot product (src/model/mod.rs:430-447, src/loader/parameters.rs:551-594).
-// The two share no code and no structure; tests require them to agree before either judges
-// the engine.  Nothing here was checked against a run of the reference (no Rust toolchain
+// The two share no code and no structure; tests require them to agree before either is used
+// to check the engine.  Nothing here was checked against a run of the reference (no Rust toolchain
 // where this is built): it rests on the cited formulas.
 //
 //   mistral_plain_onetoken <model_dir> <tokens.txt> <logits.f32>     logits [n, vocab] of one sequence
