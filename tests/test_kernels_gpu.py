@@ -588,3 +588,20 @@ def test_random_weights_same_bits_on_host_and_device(dtype, shape, integer):
     assert dev.is_cuda and dev.dtype == host.dtype and dev.shape == host.shape
     assert torch.equal(dev.cpu(), host)
     assert not torch.equal(host, random_tensor("some.tensor.weight", spec, 13, dtype, "cpu"))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("stored", [torch.float32, torch.bfloat16, torch.float16])
+def test_weight_conversion_on_the_device(dtype, stored):
+    """A stored tensor becomes the activation type where the kernels read it: widening is exact,
+    rounding to bfloat16 goes to the nearest even; stacked matrices are filled block by block."""
+    from torchless_rs_b200.parts.runtime import Runtime
+    rt = Runtime(DEV, dtype)
+    g = torch.Generator().manual_seed(7)
+    a = (torch.randn((37, 72), generator=g) * 3).to(stored)
+    b = (torch.randn((5, 72), generator=g) * 1e-3).to(stored)
+    a[0, :4] = torch.tensor([0.0, -0.0, 65504.0 if stored == torch.float16 else 3e38, 1e-7]).to(stored)
+    got = rt.stack([a, b])
+    assert got.dtype == dtype and got.shape == (42, 72) and got.is_cuda
+    assert torch.equal(got.cpu(), torch.cat([a, b]).to(dtype))
+    assert torch.equal(rt.matrix(b).cpu(), b.to(dtype))

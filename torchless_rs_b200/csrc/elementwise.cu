@@ -3,6 +3,8 @@
 // of what feeds the matrix products and of the cache.
 #include "common.cuh"
 
+#include <cuda_fp16.h>
+
 // ---------------------------------------------------------------------------
 // Embedding: x[t, :] = table[tokens[t], :]; the reference's Mistral does no more
 // (src/model/modules/embedding.rs:15-21).  Two things other arrangements put between the
@@ -418,6 +420,36 @@ extern "C" int TL_NAME(tl_silu_mul)(const float* gu, void* out, int T, int I, cu
   if (total == 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   return tl_launch(silu_mul_kernel, dim3(blocks), dim3(256), 0, stream, gu, (act_t*)out, I, total);
+}
+
+// ---------------------------------------------------------------------------
+// Weights on their way in: a stored tensor (32-bit, float16 or bfloat16, already on the device as
+// stored) becomes the activation type at its place in a matrix of the model, so that stacked
+// matrices (q/k/v; gate and up) are filled row block by row block without a joined copy.
+// bfloat16 to 32-bit and float16 to 32-bit are exact (the reference widens the same way,
+// src/loader/formats/safetensors.rs:367-390); to bfloat16 rounds to nearest even.
+// ---------------------------------------------------------------------------
+template <typename S> __device__ __forceinline__ float widen(S v);
+template <> __device__ __forceinline__ float widen<float>(float v) { return v; }
+template <> __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float widen<__half>(__half v) { return __half2float(v); }
+
+template <typename S>
+__global__ void convert_kernel(const S* __restrict__ src, act_t* __restrict__ dst, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = from_f32<act_t>(widen<S>(src[i]));
+}
+
+// src_kind: 0 = 32-bit floats, 1 = bfloat16, 2 = float16.  Returns 0, a CUDA error or TL_ERR_BAD_ARG.
+extern "C" int TL_NAME(tl_convert)(const void* src, int src_kind, void* dst, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const long long want = (n + 255) / 256;
+  const unsigned blocks = (unsigned)(want < 148 * 32 ? want : 148 * 32);
+  if (src_kind == 0) convert_kernel<float><<<blocks, 256, 0, stream>>>((const float*)src, (act_t*)dst, (size_t)n);
+  else if (src_kind == 1) convert_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (act_t*)dst, (size_t)n);
+  else if (src_kind == 2) convert_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (act_t*)dst, (size_t)n);
+  else return TL_ERR_BAD_ARG;
+  return TL_LAUNCH_STATUS();
 }
 
 // ---------------------------------------------------------------------------

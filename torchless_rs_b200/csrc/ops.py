@@ -113,7 +113,7 @@ class CoreOps:
         self.act_dtype = act_dtype
         self.suffix = _SUFFIX[act_dtype]
         self.lib = build.load_library(f"core_{self.suffix}")
-        for base in ("tl_embed", "tl_softcap", "tl_advance_step", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
+        for base in ("tl_embed", "tl_softcap", "tl_advance_step", "tl_convert", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
                      "tl_gemm_generic", "tl_attn_generic"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
@@ -147,6 +147,19 @@ class CoreOps:
                               c_int(table.shape[0]), c_float(scale), _ptr(position_table),
                               _ptr(token_pos if position_table is not None else None), c_int(max_pos),
                               _stream()), "embed")
+
+    def convert_into(self, src: torch.Tensor, dst: torch.Tensor) -> None:
+        """dst (activation type, contiguous, on the device) = src (32-bit, bfloat16 or float16, the
+        same number of elements, contiguous, on the device): a weight on its way into the model."""
+        kinds = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+        if src.dtype not in kinds:
+            raise KernelError(f"convert: unsupported stored type {src.dtype}")
+        _need(dst, self.act_dtype, "convert destination")
+        if not src.is_contiguous() or src.numel() != dst.numel():
+            raise KernelError("convert: source and destination must be contiguous and of one size")
+        from ctypes import c_longlong
+        _check(self._tl_convert(_ptr(src), c_int(kinds[src.dtype]), _ptr(dst), c_longlong(dst.numel()), _stream()),
+               "convert")
 
     def advance_step(self, token_pos: torch.Tensor, seq_len: torch.Tensor) -> None:
         """Every row's position and length go up by one, on the device (a decode step of the same

@@ -78,7 +78,7 @@ class Attention:
     def load(self, weights: Dict[str, torch.Tensor]) -> None:
         p = self.prefix
         names = ["q_proj"] + (["k_proj", "v_proj"] if self.own_cache else [])
-        self.w_qkv = torch.cat([self.rt.matrix(weights[f"{p}.{n}.weight"]) for n in names], dim=0)
+        self.w_qkv = self.rt.stack([weights[f"{p}.{n}.weight"] for n in names])
         self.w_o = self.rt.matrix(weights[f"{p}.o_proj.weight"])
 
     def cache_request(self):

@@ -44,8 +44,7 @@ class SwiGLU:
 
     def load(self, weights: Dict[str, torch.Tensor]) -> None:
         p = self.prefix
-        self.w_gate_up = torch.cat([self.rt.matrix(weights[f"{p}.gate_proj.weight"]),
-                                    self.rt.matrix(weights[f"{p}.up_proj.weight"])], dim=0)
+        self.w_gate_up = self.rt.stack([weights[f"{p}.gate_proj.weight"], weights[f"{p}.up_proj.weight"]])
         self.w_down = self.rt.matrix(weights[f"{p}.down_proj.weight"])
 
     accepts_carry = True   # `xn` may be a NormCarry; `emit` may ask for the next norm's input

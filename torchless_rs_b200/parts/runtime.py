@@ -56,7 +56,28 @@ class Runtime:
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
         """A weight matrix or table as the matrix kernels read it: on the device, in
         the activation type."""
-        return t.to(device=self.device, dtype=self.act_dtype).contiguous()
+        return self.stack([t])
+
+    def stack(self, tensors) -> torch.Tensor:
+        """Several stored matrices of one width, one below the other, as one matrix on the device in
+        the activation type (q, k and v; gate and up).  Each is copied to the device as stored and
+        converted at its place by a kernel; no joined copy is made."""
+        width = tensors[0].shape[1:]
+        for t in tensors:
+            if t.shape[1:] != width:
+                raise ValueError("stacked matrices must have one width")
+        rows = sum(int(t.shape[0]) for t in tensors)
+        out = torch.empty((rows, *width), dtype=self.act_dtype, device=self.device)
+        at = 0
+        for t in tensors:
+            n = int(t.shape[0])
+            raw = t.contiguous().to(self.device)          # as stored
+            if raw.dtype == self.act_dtype:
+                out[at:at + n].copy_(raw)
+            else:
+                self.ops.convert_into(raw, out[at:at + n])
+            at += n
+        return out
 
     def vector(self, t: torch.Tensor) -> torch.Tensor:
         """A norm weight: 32-bit if it was stored so or if the whole model runs in
