@@ -3,6 +3,7 @@
     python -m torchless_rs_b200.measure gemm M N K MODE [--iters I]
     python -m torchless_rs_b200.measure attn-decode BATCH CONTEXT [--iters I]
     python -m torchless_rs_b200.measure attn-prefill TOKENS [--iters I]
+    python -m torchless_rs_b200.measure elementwise TOKENS [--iters I]
     python -m torchless_rs_b200.measure step BATCH CONTEXT PREFILL_TOKENS [--layers L] [--iters I]
     python -m torchless_rs_b200.measure timeline BATCH CONTEXT [--layers L]
 
@@ -105,6 +106,50 @@ def attn_prefill(T: int, iters: int, nh=32, nkv=8, hd=128) -> None:
                                        1 / math.sqrt(hd), variant=variant), iters)
         print(f"attn-prefill tokens={T} kernel={variant}: {us:.2f} us, "
               f"{2.0 * nh * hd * T * T / us / 1e6:.1f} TFLOP/s (causal half counted), error word {att.take_error()}")
+
+
+def elementwise(T: int, iters: int, H=4096, nh=32, nkv=8, hd=128) -> None:
+    """The norm kernel and the rotation + cache write kernel of a prefill step of T tokens, each with inputs
+    rotated through more than the L2 cache holds and with one input over and over (as in a step, where the
+    kernel before has just written it)."""
+    from .csrc import ops
+    o = ops.core_ops(torch.bfloat16)
+    copies = max(2, int(400e6 // (T * H * 4)) + 1)
+    xs = [torch.randn((T, H), device="cuda") for _ in range(copies)]
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty((T, H), device="cuda", dtype=torch.bfloat16)
+    st = {"i": 0}
+
+    def norm(rotate):
+        o.rmsnorm(xs[st["i"] % copies if rotate else 0], w, 1e-5, y)
+        st["i"] += 1
+    byts = T * H * 6.0
+    for rotate in (True, False):
+        us = _time(lambda: norm(rotate), iters)
+        print(f"rmsnorm {T} x {H}, {'inputs from HBM' if rotate else 'input in L2'}: {us:.2f} us, {byts / us / 1e3:.0f} GB/s")
+    cols = (nh + 2 * nkv) * hd
+    copies = max(2, int(400e6 // (T * cols * 4)) + 1)
+    qkvs = [torch.randn((T, cols), device="cuda") for _ in range(copies)]
+    q = torch.empty((T, nh * hd), device="cuda", dtype=torch.bfloat16)
+    pages = (T + 63) // 64
+    kp = torch.zeros((pages, nkv, 64, hd), device="cuda", dtype=torch.bfloat16)
+    vp = torch.zeros((pages, nkv, hd, 64), device="cuda", dtype=torch.bfloat16)
+    pos = torch.arange(T, dtype=torch.int32, device="cuda")
+    seq = torch.zeros(T, dtype=torch.int32, device="cuda")
+    slot = torch.zeros(1, dtype=torch.int32, device="cuda")
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, pages)
+    half = hd // 2
+    inv = (1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64),
+                           torch.arange(half, dtype=torch.float64) / half)).float().cuda()
+
+    def rope(rotate):
+        o.rope_cache_write(qkvs[st["i"] % copies if rotate else 0], q, kp, vp, pos, seq, slot, table, inv, 0, nh, nkv, hd)
+        st["i"] += 1
+    byts = T * cols * 6.0
+    for rotate in (True, False):
+        us = _time(lambda: rope(rotate), iters)
+        print(f"rotation + cache write, {T} tokens, {'inputs from HBM' if rotate else 'input in L2'}: {us:.2f} us, "
+              f"{byts / us / 1e3:.0f} GB/s")
 
 
 MISTRAL_7B_SIZES = {
@@ -231,7 +276,7 @@ def timeline(B: int, context: int, layers: int) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "step", "timeline"])
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "step", "timeline"])
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
@@ -243,6 +288,8 @@ def main() -> None:
         attention_bf16.decode_splits = lambda *args, **kw: a.splits
     if a.what == "gemm":
         gemm(*a.sizes[:4], a.iters)
+    elif a.what == "elementwise":
+        elementwise(a.sizes[0], min(a.iters, 24))
     elif a.what == "timeline":
         timeline(a.sizes[0], a.sizes[1], a.layers)
     elif a.what == "step":
