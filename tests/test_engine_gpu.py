@@ -222,3 +222,31 @@ def test_steady_decode_steps_advance_their_state_on_the_device(tiny):
     ref_a, ref_b = tiny.reference(a[:83]), tiny.reference(b[:78])
     assert_close(np.concatenate(got[0]), ref_a[9:], tiny.dtype, "first sequence")
     assert_close(np.concatenate(got[1]), ref_b[4:], tiny.dtype, "second sequence")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 1500])
+def test_long_context(dtype, window):
+    """A prompt of 2500 tokens in two chunks (2000 + 500: dozens of pages per sequence, the window's
+    edge inside the prompt, pages given back between the chunks), a short second sequence beside it,
+    then 40 tokens decoded one by one at a context where the keys of a sequence are shared among
+    many blocks."""
+    from tiny import TINY_D
+    cfg = dict(TINY_D, sliding_window=window)
+    tm = TinyModel("long", dtype, seed=77, max_tokens=4096, cfg=cfg)
+    a, b = _requests(tm, [2540, 75], 61)
+    sa, sb = tm.engine.start_sequences(2)
+    got_a = [tm.step_np([sa], [a[:2000]], "all")[-50:]]
+    out = tm.step_np([sa, sb], [a[2000:2500], b[:35]], "all")
+    got_a.append(out[:500]); got_b = [out[500:]]
+    for i in range(40):
+        out = tm.step_np([sa, sb], [[a[2500 + i]], [b[35 + i]]], "last")
+        got_a.append(out[0:1]); got_b.append(out[1:2])
+    tm.engine.cache.check()
+    if window:
+        g = tm.engine.cache.paged[0]
+        assert g.first_live[sa] == (2540 - window + 1) // 64     # the pages before the window went back
+    tm.engine.end_sequences([sa, sb])
+    ref_a, ref_b = tm.reference(a), tm.reference(b)
+    assert_close(np.concatenate(got_a), ref_a[1950:], dtype, "long sequence")
+    assert_close(np.concatenate(got_b), ref_b, dtype, "short sequence beside it")
