@@ -219,7 +219,7 @@ def prefill_timed(model, lengths, repeats: int = 3):
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        eng.step(slots, toks, "last")
+        eng.prefill(slots, toks)   # what `generate` calls: many tokens go in several steps
         e1.record()
         torch.cuda.synchronize()
         eng.end_sequences(slots)

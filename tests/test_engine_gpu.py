@@ -138,6 +138,28 @@ def test_prompt_in_chunks_on_a_slot_that_holds_tokens(tiny):
     assert_close(np.concatenate(got), tiny.reference(toks), tiny.dtype, "prompt in chunks")
 
 
+def test_prefill_in_several_steps_gives_each_prompts_last_logits(tiny):
+    """`Engine.prefill` with a small number of tokens per step: four prompts of unequal lengths go
+    in steps of 128 tokens each, the shorter ones run out earlier, and every prompt's last logits
+    are those of the plain implementation; then the sequences decode one token together."""
+    reqs = _requests(tiny, [300, 129, 40, 256], 41)
+    slots = tiny.engine.start_sequences(4)
+    got = tiny.engine.prefill(slots, reqs, tokens_per_step=256).cpu().numpy().copy()
+    tiny.engine.cache.check()
+    for i, r in enumerate(reqs):
+        assert_close(got[i:i + 1], tiny.reference(r)[-1:], tiny.dtype, f"prefill in steps, prompt {i}")
+    nxt = [int(g.argmax()) for g in got]
+    dec = tiny.step_np(slots, [[t] for t in nxt], "last")
+    tiny.engine.end_sequences(slots)
+    for i, r in enumerate(reqs):
+        assert_close(dec[i:i + 1], tiny.reference(list(r) + [nxt[i]])[-1:], tiny.dtype, f"decode after, {i}")
+    # under the limit it is one step, and the same numbers
+    slots = tiny.engine.start_sequences(4)
+    one = tiny.engine.prefill(slots, reqs, tokens_per_step=4096).cpu().numpy().copy()
+    tiny.engine.end_sequences(slots)
+    assert_close(one, got, tiny.dtype, "one step against several")
+
+
 def test_decode_across_a_length_bucket(tiny):
     """Decoding from 250 to 520 tokens: the recorded graph's key and the split of the keys
     among blocks change at 256 and at 512."""

@@ -231,3 +231,25 @@ def test_a_set_error_word_is_raised_and_cleared():
         ops.check_kernel_errors()
     finally:
         ops._error_words.pop("toy_library")
+
+
+def test_an_engine_that_offers_prefill_gets_the_prompts_through_it():
+    """The loop hands a batch's prompts to `prefill` where the engine has one (it may cut them into
+    several steps) and decodes with `step` afterwards; the tokens are the same."""
+    class WithPrefill(ScriptedEngine):
+        def prefill(self, slots, prompts):
+            for a in range(0, max(len(p) for p in prompts), 2):       # two tokens of each prompt a step
+                rows = [(s, p[a:a + 2]) for s, p in zip(slots, prompts) if p[a:a + 2]]
+                self.step([s for s, _ in rows], [t for _, t in rows])
+            return [(s, self.length[s], p[-1]) for s, p in zip(slots, prompts)]
+
+    prompts = [[1, 2, 3, 4, 5], [9], [7, 7, 7]]
+    eng = WithPrefill(n_slots=3)
+    res = generate(eng, select, prompts, 6, SamplingParams.greedy(), set(), cache_tokens=10 ** 6, max_batch=3,
+                   to_host=list)
+    for i, p in enumerate(prompts):
+        assert res[i].tokens == expected(p, 6, set())[0], i
+    steps = [e for e in eng.log if e[0] == "step"]
+    assert [e[2] for e in steps[:3]] == [(2, 1, 2), (2, 1), (1,)]      # the prompts, cut
+    assert all(set(e[2]) == {1} for e in steps[3:])                    # then one token each
+    assert not eng.held

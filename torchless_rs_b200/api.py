@@ -101,6 +101,10 @@ class Model:
     def step(self, slots, tokens, want="last"):
         return self.engine.step(slots, tokens, want)
 
+    def prefill(self, slots, prompts, tokens_per_step=None):
+        """The logits at each prompt's last token; many tokens go in several steps."""
+        return self.engine.prefill(slots, prompts, tokens_per_step)
+
     def start_sequences(self, count: int):
         return self.engine.start_sequences(count)
 

@@ -137,7 +137,12 @@ def generate(engine, select: Callable, prompts: Sequence[Sequence[int]], max_tok
                 engine.end_sequences(ss)   # ends earlier: its slot is free at once
         try:
             live = list(zip(batch, slots))          # (request index, slot), in request order
-            logits = engine.step([s for _, s in live], [list(prompts[i]) for i in batch], want="last")
+            # an engine that offers `prefill` feeds long prompts in several steps (same logits)
+            feed = getattr(engine, "prefill", None)
+            if feed is not None:
+                logits = feed([s for _, s in live], [list(prompts[i]) for i in batch])
+            else:
+                logits = engine.step([s for _, s in live], [list(prompts[i]) for i in batch], want="last")
             selected = select(logits, params, uniforms_for([i for i, _ in live], 0))
             handle = reader.start(selected)
             where = list(range(len(live)))          # place of each live sequence in `selected`
