@@ -246,6 +246,57 @@ def test_steady_decode_steps_advance_their_state_on_the_device(tiny):
     assert_close(np.concatenate(got[1]), ref_b[4:], tiny.dtype, "second sequence")
 
 
+def test_rows_that_end_are_dropped_on_the_device(tiny):
+    """Five sequences decode with their tokens taken from a device buffer.  Two of them end, then the
+    rest take their tokens from other places of the buffer, then one more ends and the order of the
+    rows is turned round: the engine makes each such step's arrays with a kernel from the step
+    before (no layout on the host, nothing copied but page-table rows), and every sequence's logits
+    are the plain implementation's."""
+    import torch
+    lens = [70, 66, 90, 40, 75]
+    reqs = _requests(tiny, lens, 61)
+    slots = tiny.engine.start_sequences(5)
+    pre = [30, 3, 64, 20, 1]
+    out = tiny.step_np(slots, [r[:p] for r, p in zip(reqs, pre)], "last")
+    got = {i: [out[i:i + 1]] for i in range(5)}
+    fed = list(pre)
+    src = torch.zeros(8, dtype=torch.int32, device="cuda:0")
+
+    def run(rows, places):
+        vals = [0] * 8
+        for i, pl in zip(rows, places):
+            vals[pl] = reqs[i][fed[i]]
+        src.copy_(torch.tensor(vals, dtype=torch.int32))
+        o = tiny.engine.step([slots[i] for i in rows], None, "last", from_device=(src, places))
+        o = o.float().cpu().numpy().copy()
+        for j, i in enumerate(rows):
+            got[i].append(o[j:j + 1])
+            fed[i] += 1
+
+    eng = tiny.engine
+    run([0, 1, 2, 3, 4], [0, 1, 2, 3, 4])            # laid out on the host
+    staged, copied, regrouped = eng.stager.staged, eng.stager.bytes_copied, eng.steps_regrouped_on_device
+    for _ in range(3):
+        run([0, 1, 2, 3, 4], [0, 1, 2, 3, 4])        # advanced
+    eng.end_sequences([slots[1], slots[3]])
+    run([0, 2, 4], [0, 2, 4])                        # two rows fewer
+    run([0, 2, 4], [0, 1, 2])                        # the same rows, other places
+    for _ in range(12):
+        run([0, 2, 4], [0, 1, 2])                    # advanced (sequence 2 takes a new page on the way)
+    eng.end_sequences([slots[0]])
+    run([4, 2], [7, 5])                              # one fewer, and the other way round
+    for _ in range(5):
+        run([4, 2], [7, 5])
+    assert eng.steps_regrouped_on_device - regrouped == 3
+    assert eng.stager.bytes_copied == copied, "a step was laid out on the host"
+    assert eng.stager.staged - staged == 3
+    eng.cache.check()
+    eng.end_sequences([slots[2], slots[4]])
+    for i in range(5):
+        assert_close(np.concatenate(got[i]), tiny.reference(reqs[i][:fed[i]])[pre[i] - 1:], tiny.dtype,
+                     f"sequence {i}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [None, 1500])
 def test_long_context(dtype, window):

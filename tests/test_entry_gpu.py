@@ -40,9 +40,20 @@ def test_greedy_generation_equals_plain(name, dtype):
     # a stop token ends its sequence early and is not emitted; the others go on
     first = res[1].tokens
     stop = first[3]
+    regrouped, copied = tm.engine.steps_regrouped_on_device, tm.engine.stager.bytes_copied
     res2 = tm.model.generate(prompts, max_tokens=12, temperature=0.0, stop_ids=[stop])
     want = _plain_greedy(tm, prompts[1], 12, stop=(stop,))
     assert res2[1].tokens == want and res2[1].stopped_at_eos
+    for i in (0, 2):
+        assert res2[i].tokens == _plain_greedy(tm, prompts[i], 12, stop=(stop,)), f"prompt {i} beside the one that ended"
+    # the batch shrank on the way: the steps after that were set up by a kernel, and the host laid
+    # out the prompts' step and the first decode step only
+    if not all(r.stopped_at_eos for r in res2) and len(want) < 10:
+        assert tm.engine.steps_regrouped_on_device > regrouped
+        T, B = sum(len(p) for p in prompts), len(prompts)
+        pad = lambda n: (n + 3) // 4 * 4
+        layout = lambda t: 4 * (4 * pad(t) + 3 * pad(B) + pad(B + 1))     # bytes of one step's eight arrays
+        assert tm.engine.stager.bytes_copied - copied == layout(T) + layout(B)
     assert tm.engine.cache.slots.held_count == 0
     tm.engine.cache.check()
 

@@ -472,4 +472,57 @@ extern "C" int TL_NAME(tl_advance_step)(int* token_pos, int* seq_len, int n, cud
   return tl_launch(advance_step_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, token_pos, seq_len, n);
 }
 
+// ---------------------------------------------------------------------------
+// A decode step of some of the rows of the decode step before, in any order (sequences have ended,
+// or the rows take their tokens from other places of the sampler's output): the new step's arrays
+// are made here from the old ones, each kept row's position and length one higher.  `base` is the
+// buffer that holds both layouts (they overlap), so one block reads all it needs before any thread
+// writes.  off[]: where the eight arrays of the new layout start in `base`, in the order tokens,
+// token_seq, token_pos, seq_slot, seq_start, seq_len, want_rows, token_from.
+// ---------------------------------------------------------------------------
+#define REGROUP_MAX_ROWS 256
+struct RegroupRows { unsigned short keep[REGROUP_MAX_ROWS]; unsigned short from[REGROUP_MAX_ROWS]; };
+struct RegroupOffsets { int off[8]; };
+
+__global__ void __launch_bounds__(REGROUP_MAX_ROWS)
+regroup_step_kernel(const int* old_pos, const int* old_len, const int* old_slot, int* base,
+                    const RegroupOffsets o, int n, const __grid_constant__ RegroupRows rows) {
+  pdl_wait();   // the step before still reads the old arrays
+  pdl_launch_dependents();
+  const int j = threadIdx.x;
+  int pos = 0, len = 0, slot = 0;
+  if (j < n) {
+    const int r = rows.keep[j];
+    pos = old_pos[r];
+    len = old_len[r];
+    slot = old_slot[r];
+  }
+  __syncthreads();
+  if (j < n) {
+    base[o.off[0] + j] = 0;
+    base[o.off[1] + j] = j;
+    base[o.off[2] + j] = pos + 1;
+    base[o.off[3] + j] = slot;
+    base[o.off[4] + j] = j;
+    base[o.off[5] + j] = len + 1;
+    base[o.off[6] + j] = j;
+    base[o.off[7] + j] = rows.from[j];
+  }
+  if (j == 0) base[o.off[4] + n] = n;
+}
+
+extern "C" int TL_NAME(tl_regroup_step)(const int* old_pos, const int* old_len, const int* old_slot, int* base,
+                                        const int* offsets, int n, const unsigned short* keep,
+                                        const unsigned short* from, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n > REGROUP_MAX_ROWS) return -2;
+  RegroupRows rows;
+  RegroupOffsets o;
+  for (int i = 0; i < n; ++i) { rows.keep[i] = keep[i]; rows.from[i] = from[i]; }
+  for (int i = n; i < REGROUP_MAX_ROWS; ++i) rows.keep[i] = rows.from[i] = 0;
+  for (int i = 0; i < 8; ++i) o.off[i] = offsets[i];
+  return tl_launch(regroup_step_kernel, dim3(1), dim3(REGROUP_MAX_ROWS), 0, stream, old_pos, old_len, old_slot,
+                   base, o, n, rows);
+}
+
 TL_TRACE_EXPORT(elementwise)

@@ -113,7 +113,7 @@ class CoreOps:
         self.act_dtype = act_dtype
         self.suffix = _SUFFIX[act_dtype]
         self.lib = build.load_library(f"core_{self.suffix}")
-        for base in ("tl_embed", "tl_softcap", "tl_advance_step", "tl_convert", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
+        for base in ("tl_embed", "tl_softcap", "tl_advance_step", "tl_regroup_step", "tl_convert", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
                      "tl_gemm_generic", "tl_attn_generic"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
@@ -170,6 +170,31 @@ class CoreOps:
             raise KernelError("advance_step: one position and one length per row are needed")
         _check(self._tl_advance_step(_ptr(token_pos), _ptr(seq_len), c_int(seq_len.numel()), _stream()),
                "advance_step")
+
+    REGROUP_MAX_ROWS = 256
+
+    def regroup_step(self, old_pos: torch.Tensor, old_len: torch.Tensor, old_slot: torch.Tensor,
+                     base: torch.Tensor, offsets, keep, token_from) -> None:
+        """The arrays of a decode step of the rows `keep` of the decode step before (whose positions,
+        lengths and slots are `old_*`), written into `base` at `offsets` (eight starts, in the order
+        tokens, token_seq, token_pos, seq_slot, seq_start, seq_len, want_rows, token_from); row j takes
+        its token from place token_from[j] of the sampler's output.  The old arrays may lie in `base`."""
+        from ctypes import c_ushort
+        n = len(keep)
+        if n > self.REGROUP_MAX_ROWS or len(token_from) != n or len(offsets) != 8:
+            raise KernelError("regroup_step: at most 256 rows, one source place per row, eight offsets")
+        if n and (max(keep) >= old_pos.numel() or max(keep) > 65535 or max(token_from) > 65535
+                  or min(keep) < 0 or min(token_from) < 0):
+            raise KernelError("regroup_step: a row or a source place is out of range")
+        for t, what in ((old_pos, "positions"), (old_len, "lengths"), (old_slot, "slots"), (base, "buffer")):
+            _need(t, torch.int32, "regroup " + what)
+        if max(offsets) + n + 1 > base.numel():
+            raise KernelError("regroup_step: the new layout does not fit the buffer")
+        _check(self._tl_regroup_step(_ptr(old_pos), _ptr(old_len), _ptr(old_slot), _ptr(base),
+                                     (c_int * 8)(*[int(o) for o in offsets]), c_int(n),
+                                     (c_ushort * max(n, 1))(*[int(k) for k in keep]),
+                                     (c_ushort * max(n, 1))(*[int(f) for f in token_from]), _stream()),
+               "regroup_step")
 
     def softcap(self, logits: torch.Tensor, cap: float) -> None:
         """logits <- cap * tanh(logits / cap), in place."""

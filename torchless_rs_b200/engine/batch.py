@@ -95,13 +95,35 @@ class BatchStager:
         self.dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         self.capacity = cap
 
-    def stage(self, arrays: dict, slots, past_lens, is_decode: bool) -> StepBatch:
-        sizes = [int(arrays[f].shape[0]) for f in self.FIELDS]
-        # every field starts on a 4-element (16-byte) boundary
+    @staticmethod
+    def _offsets(sizes):
+        """Where each field starts in the buffer: on a 4-element (16-byte) boundary."""
         offs, total = [], 0
         for s in sizes:
             offs.append(total)
             total += (s + 3) // 4 * 4
+        return offs, total
+
+    def regroup(self, before: StepBatch, keep, token_from, slots, past_lens, new_lens, ops) -> StepBatch:
+        """The decode step of the rows `keep` of the decode step `before`, whose arrays the device buffer
+        still holds: a kernel writes the new step's arrays from them (nothing is copied from the host).
+        Row j takes its token from place token_from[j] of the sampler's output."""
+        n = len(keep)
+        sizes = [n, n, n, n, n + 1, n, n, n]
+        offs, total = self._offsets(sizes)
+        self._ensure(max(total, 1))
+        self.staged += 1
+        ops.regroup_step(before.token_pos, before.seq_len, before.seq_slot, self.dev, offs, keep, token_from)
+        views = {f: self.dev[o:o + s] for f, o, s in zip(self.FIELDS, offs, sizes)}
+        max_len = max(new_lens)
+        return StepBatch(
+            n_tokens=n, n_seqs=n, n_want=n, is_decode=True, max_new=1, max_len=max_len,
+            len_bucket=max(256, 1 << max(max_len - 1, 0).bit_length()),
+            slots=list(slots), past_lens=list(past_lens), new_lens=list(new_lens), **views)
+
+    def stage(self, arrays: dict, slots, past_lens, is_decode: bool) -> StepBatch:
+        sizes = [int(arrays[f].shape[0]) for f in self.FIELDS]
+        offs, total = self._offsets(sizes)
         self._ensure(max(total, 1))
         self.staged += 1
         self.turn = (self.turn + 1) % self.RING

@@ -47,6 +47,7 @@ class Engine:
         self._seen = set()     # keys that have run once without a graph
         self._steady = None    # (key, staged count, batch) of the last decode step fed from the device
         self.steps_advanced_on_device = 0
+        self.steps_regrouped_on_device = 0   # decode steps whose rows a kernel chose from the step before
 
     # ---- sequences -------------------------------------------------------------------
     def start_sequences(self, count: int) -> List[int]:
@@ -135,6 +136,23 @@ class Engine:
                 logits = self._forward(batch)
                 self.cache.commit(slots, new_lens)
                 return logits
+            # Some of that step's sequences (others have ended), or the same ones taking their tokens
+            # from other places: a kernel makes the new step's arrays from the old ones.
+            if st is not None and st[1] == self.stager.staged and B <= self.rt.ops.REGROUP_MAX_ROWS:
+                row_of = {s: r for r, s in enumerate(st[2].slots)}
+                keep = [row_of.get(s, -1) for s in slots]
+                if min(keep) >= 0 and max(keep) < 65536 and len(set(slots)) == B and \
+                        all(st[2].new_lens[r] == p for r, p in zip(keep, past)) and \
+                        all(0 <= int(i) < 65536 for i in src_index):
+                    self.cache.prepare(slots, new_lens)
+                    batch = self.stager.regroup(st[2], keep, [int(i) for i in src_index], slots, past,
+                                                new_lens, self.rt.ops)
+                    batch.token_src = token_src
+                    self._steady = (steady_key, self.stager.staged, batch)
+                    self.steps_regrouped_on_device += 1
+                    logits = self._forward(batch)
+                    self.cache.commit(slots, new_lens)
+                    return logits
         arrays = layout_step(past, counts, slots, tokens, want)
         if token_src is not None:
             arrays["token_from"] = np.asarray(src_index, dtype=np.int32)
