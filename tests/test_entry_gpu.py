@@ -200,3 +200,9 @@ def test_model_drawn_on_the_device_is_the_folder_written_from_the_same_seed(tmp_
     m2 = tl.load(d, dtype="float32", max_tokens=256)
     (s,) = m2.start_sequences(1)
     assert np.array_equal(m2.step([s], [toks], "all").cpu().numpy(), got)
+    # and `load(..., random_weights=True)` needs config.json only
+    import os
+    os.remove(os.path.join(d, "model.safetensors"))
+    m3 = tl.load(d, dtype="float32", max_tokens=256, random_weights=True, seed=21)
+    (s,) = m3.start_sequences(1)
+    assert np.array_equal(m3.step([s], [toks], "all").cpu().numpy(), got)

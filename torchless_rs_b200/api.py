@@ -126,10 +126,15 @@ def _default_max_tokens(config) -> int:
 
 def load(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
          max_tokens: Optional[int] = None, max_batch: Optional[int] = None,
-         max_seq_len: Optional[int] = None, device: str = "cuda:0") -> Model:
+         max_seq_len: Optional[int] = None, device: str = "cuda:0",
+         random_weights: bool = False, seed: int = 0) -> Model:
     """Loads `config.json` and the safetensors weights of `model_dir`.  The model
-    class is chosen by config.json through the architecture registry."""
+    class is chosen by config.json through the architecture registry.  With
+    `random_weights` the folder needs config.json only: the weights are drawn from `seed`
+    (the same values that `write_random_model` writes for that seed)."""
     config = load_config(model_dir)
+    if random_weights:
+        return from_random(config, seed, dtype, max_tokens, max_batch, max_seq_len, device)
     spec = config.model_spec()
     rt = Runtime(device, parse_dtype(dtype))
     weights, source = load_checked(model_dir, expected_tensors(spec), rt.act_dtype)
