@@ -144,7 +144,10 @@ def test_prefill_in_several_steps_gives_each_prompts_last_logits(tiny):
     are those of the plain implementation; then the sequences decode one token together."""
     reqs = _requests(tiny, [300, 129, 40, 256], 41)
     slots = tiny.engine.start_sequences(4)
+    staged = tiny.engine.stager.staged
     got = tiny.engine.prefill(slots, reqs, tokens_per_step=256).cpu().numpy().copy()
+    # 128 + 128 + 44, 129 at once (one token gets no step of its own), 40, 128 + 128
+    assert tiny.engine.stager.staged - staged == 3
     tiny.engine.cache.check()
     for i, r in enumerate(reqs):
         assert_close(got[i:i + 1], tiny.reference(r)[-1:], tiny.dtype, f"prefill in steps, prompt {i}")

@@ -40,6 +40,7 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <type_traits>
 
 #define TILE_N 128        // weight rows per tile (M of the instruction)
 #define TILE_K 64         // K elements per shared memory tile (128 bytes)
@@ -445,31 +446,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             nw4[e] = args.nw_is_f32 ? ((const float*)args.nw)[n4 + e]
                                     : __bfloat162float(((const __nv_bfloat16*)args.nw)[n4 + e]);
         }
-        for (int k0 = warp; rank + k0 * splits < cols; k0 += 8) {
-          float4 v[2], u[2], prev[2];
-          int cc[2];
+        // One turn of a warp: NC columns, the partial tiles of all splits requested before any is
+        // added (a turn costs one round trip through the cluster's shared memory whatever it moves:
+        // with two columns a turn, a tile of 64 tokens in two splits took four turns).  The number
+        // of splits is a compile-time constant S where it is 2, 4 or 8 (S = 0: any other), so that
+        // the loads sit in registers; the sums run in the order of the splits in every case.
+        auto reduce_turns = [&](auto s_tag) {
+        constexpr int S = decltype(s_tag)::value;
+        constexpr int NC = S == 0 ? 2 : ((SWIGLU ? 8 : 16) / S);
+        for (int k0 = warp; rank + k0 * splits < cols; k0 += 4 * NC) {
+          float4 v[NC], u[NC], prev[NC];
+          int cc[NC];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < NC; ++h) {
             const int c = rank + (k0 + 4 * h) * splits;
             cc[h] = c < cols ? c : -1;
             v[h] = u[h] = prev[h] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (cc[h] >= 0 && accum && live4)
               prev[h] = *reinterpret_cast<const float4*>((const float*)args.C + (size_t)(m0 + c) * args.ldc + n4);
           }
+          if constexpr (S > 0) {
+            float4 pa[NC][S], pb[SWIGLU ? NC : 1][SWIGLU ? S : 1];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (cc[h] < 0) continue;
-            for (int sp = 0; sp < splits; ++sp) {
-              const float4 a = ld_remote_f32x4(red_s + (uint32_t)(cc[h] * TILE_N + 4 * lane) * 4u, (uint32_t)sp);
-              v[h].x += a.x; v[h].y += a.y; v[h].z += a.z; v[h].w += a.w;
-              if (SWIGLU) {
-                const float4 b = ld_remote_f32x4(red_s + (uint32_t)((BN + cc[h]) * TILE_N + 4 * lane) * 4u, (uint32_t)sp);
-                u[h].x += b.x; u[h].y += b.y; u[h].z += b.z; u[h].w += b.w;
+            for (int h = 0; h < NC; ++h) {
+#pragma unroll
+              for (int sp = 0; sp < S; ++sp) {
+                pa[h][sp] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (SWIGLU) pb[h][sp] = pa[h][sp];
+                if (cc[h] < 0) continue;
+                pa[h][sp] = ld_remote_f32x4(red_s + (uint32_t)(cc[h] * TILE_N + 4 * lane) * 4u, (uint32_t)sp);
+                if (SWIGLU)
+                  pb[h][sp] = ld_remote_f32x4(red_s + (uint32_t)((BN + cc[h]) * TILE_N + 4 * lane) * 4u, (uint32_t)sp);
+              }
+            }
+#pragma unroll
+            for (int h = 0; h < NC; ++h) {
+#pragma unroll
+              for (int sp = 0; sp < S; ++sp) {
+                v[h].x += pa[h][sp].x; v[h].y += pa[h][sp].y; v[h].z += pa[h][sp].z; v[h].w += pa[h][sp].w;
+                if (SWIGLU) { u[h].x += pb[h][sp].x; u[h].y += pb[h][sp].y; u[h].z += pb[h][sp].z; u[h].w += pb[h][sp].w; }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int h = 0; h < NC; ++h) {
+              if (cc[h] < 0) continue;
+              for (int sp = 0; sp < splits; ++sp) {
+                const float4 a = ld_remote_f32x4(red_s + (uint32_t)(cc[h] * TILE_N + 4 * lane) * 4u, (uint32_t)sp);
+                v[h].x += a.x; v[h].y += a.y; v[h].z += a.z; v[h].w += a.w;
+                if (SWIGLU) {
+                  const float4 b = ld_remote_f32x4(red_s + (uint32_t)((BN + cc[h]) * TILE_N + 4 * lane) * 4u, (uint32_t)sp);
+                  u[h].x += b.x; u[h].y += b.y; u[h].z += b.z; u[h].w += b.w;
+                }
               }
             }
           }
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < NC; ++h) {
             if (cc[h] < 0) continue;
             const int c = cc[h];
             float val[4] = {v[h].x, v[h].y, v[h].z, v[h].w}, up[4] = {u[h].x, u[h].y, u[h].z, u[h].w};
@@ -560,6 +593,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (lane == 0) args.ss_out[(size_t)(m0 + c) * gridDim.x + blockIdx.x] = sq;
             }
           }
+        }
+        };
+        // Only for token tiles of 64 and more, where a block has many columns to reduce: the loads
+        // in flight cost some 40 registers, and with 121 instead of 80 registers a block of the
+        // next kernel no longer fits beside two of this one (a decode step at batch 8 took 3.63
+        // instead of 3.57 ms when the tiles of 16 tokens were compiled this way too).
+        if constexpr (BN >= 64) {
+          if (splits == 8) reduce_turns(std::integral_constant<int, 8>{});
+          else if (splits == 4) reduce_turns(std::integral_constant<int, 4>{});
+          else if (splits == 2) reduce_turns(std::integral_constant<int, 2>{});
+          else reduce_turns(std::integral_constant<int, 0>{});
+        } else {
+          reduce_turns(std::integral_constant<int, 0>{});
         }
       } else {
       // columns rank, rank + splits, ... in groups of 8, so that the loads of a group (old C,
@@ -1383,15 +1429,13 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
     // keeps every block resident at once
     while (splits * 2 <= MAX_SPLITS && tiles * splits * 2 <= slots && splits * 2 <= kb_np / 2)
       splits *= 2;
-    // token tiles of 128: the reduction of so wide a tile costs about as much as 40 K-blocks
-    // of 64 elements (measured), so the split has to save more than that
-    if (!two_per_sm && ((kb_np + splits - 1) / splits) * kstep64 + 40 >= kb_total) splits = 1;
+    // token tiles of 128: the reduction of so wide a tile costs about as much as 16 K-blocks of 64
+    // elements (measured: q/k/v at 128 tokens 19.0 us unsplit, 17.0 us in two splits), so the split has
+    // to save more than that
+    if (!two_per_sm && ((kb_np + splits - 1) / splits) * kstep64 + 16 >= kb_total) splits = 1;
   }
   int kb_per_split = (kb_np + splits - 1) / splits;
   splits = (kb_np + kb_per_split - 1) / kb_per_split;   // no empty split
-  // Many tokens: the persistent kernels with two accumulators.
-  const bool persistent = M > 128 && !ss_in;
-  if (persistent) bn = swiglu ? 128 : 256;
   const int pairs = num_sms / 2;
   const int pair_n = swiglu ? 128 : 256;
   // token tiles of equal width, a multiple of 32 (300 tokens: two tiles of 160, not 256 + 44)
@@ -1408,6 +1452,15 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
       if (cost < best) { best = cost; pair_splits = sp; }
     }
   }
+  // Many tokens: the persistent kernels with two accumulators.  Not for 129 to 256 tokens of a
+  // matrix with so few rows that most pairs would idle while the one-SM kernel with its K splits
+  // fills the GPU (measured at 4096 rows and 129 / 256 tokens: K = 4096 23.1 / 29.1 us by pairs, 15.5 /
+  // 18.1 us by single SMs; K = 14336 39.2 / 47.5 against 34.5 / 38.0 us; at 5120 rows and more the pairs win).
+  bool persistent = M > 128 && !ss_in;
+  if (persistent && M <= 256 && !swiglu && tiles * splits * 5 >= (long long)num_sms * 4 &&
+      tiles_p * pair_splits * 10 <= (long long)pairs * 7)
+    persistent = false;
+  if (persistent) bn = swiglu ? 128 : 256;
   const bool use_pair = persistent;
   if (use_pair) {
     CUtensorMap pw, px;
@@ -1430,7 +1483,7 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
   // the fold and the rotation live in the few-token kernel's K-split reduction only: the
   // persistent kernels neither write xw_out / ss_out nor look at the rope arguments
   const bool emit = xw_out && ss_out && nw && mode == MODE_ACCUM_F32 && splits > 1 && !persistent &&
-                    N % 8 == 0;
+                    M <= 128 && N % 8 == 0;   // (beyond 128 tokens the products that would take the carry run by pairs)
   a.xw_out = emit ? (__nv_bfloat16*)xw_out : nullptr;
   a.nw = nw; a.nw_is_f32 = nw_is_f32; a.ss_out = emit ? ss_out : nullptr;
   if (emitted) *emitted = emit ? 1 : 0;

@@ -180,8 +180,9 @@ class Engine:
         """Feeds the prompts of sequences that start together and returns the 32-bit logits
         [sequences, vocab] at each prompt's last token (a buffer of its own, valid until the next
         call).  Prompts whose tokens together exceed `tokens_per_step` are fed in several steps, every
-        sequence going on by the same number of tokens (a multiple of the page size, at least 128)
-        until its prompt runs out; the result does not depend on the cut beyond rounding."""
+        sequence going on by the same number of tokens (a multiple of the page size, at least 128;
+        a prompt's end up to a quarter more) until its prompt runs out; the result does not depend
+        on the cut beyond rounding."""
         B = len(slots)
         budget = tokens_per_step or self.PREFILL_TOKENS_PER_STEP
         total = sum(len(p) for p in prompts)
@@ -194,7 +195,9 @@ class Engine:
             rows = [b for b in range(B) if fed[b] < len(prompts[b])]
             if not rows:
                 return out
-            toks = [list(prompts[b][fed[b]:fed[b] + chunk]) for b in rows]
+            # a prompt's last tokens do not get a step of their own: up to a quarter more goes now
+            toks = [list(prompts[b][fed[b]:fed[b] + (chunk if len(prompts[b]) - fed[b] > chunk + chunk // 4
+                                                       else len(prompts[b]))]) for b in rows]
             ends = [fed[b] + len(t) >= len(prompts[b]) for b, t in zip(rows, toks)]
             logits = self.step([slots[b] for b in rows], toks, [[len(t) - 1] if e else [] for t, e in zip(toks, ends)])
             k = 0
