@@ -6,7 +6,7 @@ import numpy as np
 import torch
 
 from plain import mistral_plain as plain
-from tiny import CONFIGS, make_model_dir, read_weights_numpy
+from tiny import CONFIGS, make_model_dir, read_weights_numpy, remove_model_dir
 
 # Stated tolerances.  32-bit: the engine and the plain implementation differ only in
 # the order of 32-bit sums.  bfloat16: activations between kernels and the cache are
@@ -41,9 +41,12 @@ class TinyModel:
         self.dtype = dtype
         if store is None:
             store = torch.float32 if dtype == "float32" else torch.bfloat16
-        self.dir = make_model_dir(self.cfg, seed, store)
-        self.weights = read_weights_numpy(self.dir)
-        self.model = tl.load(self.dir, dtype=dtype, max_tokens=max_tokens, max_batch=max_batch)
+        d = make_model_dir(self.cfg, seed, store)
+        try:
+            self.weights = read_weights_numpy(d)
+            self.model = tl.load(d, dtype=dtype, max_tokens=max_tokens, max_batch=max_batch)
+        finally:
+            remove_model_dir(d)      # the folder is needed for loading only (real sizes take a gigabyte)
         self.engine = self.model.engine
         self._ref = {}
 

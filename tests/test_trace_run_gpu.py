@@ -4,6 +4,7 @@ batch after another in a cache that only holds one; all compared with the plain
 implementation, in 32-bit and in bfloat16."""
 import json
 import os
+import shutil
 import subprocess
 import tempfile
 
@@ -40,6 +41,7 @@ def run_trace(model_dir, dtype, max_tokens, steps):
         assert os.path.exists(f) == (n > 0)
         if n:
             got[rec["step"]] = np.fromfile(f, dtype="<f4").reshape(n, vocab)
+    shutil.rmtree(out, ignore_errors=True)
     return got
 
 

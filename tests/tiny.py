@@ -8,6 +8,7 @@ is no multiple of 8; a fourth has a head size and window that the tensor-core
 attention kernels take; a sixth is wide enough for the split-K products of decode."""
 from __future__ import annotations
 
+import atexit
 import os
 import tempfile
 
@@ -70,11 +71,31 @@ REAL_SIZES = {
 CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
 
 
+_made: list = []
+
+
+def remove_model_dir(d: str) -> None:
+    """Deletes a folder that `make_model_dir` made in a temporary place."""
+    import shutil
+    shutil.rmtree(d, ignore_errors=True)
+    if d in _made:
+        _made.remove(d)
+
+
+@atexit.register
+def _remove_all() -> None:
+    for d in list(_made):
+        remove_model_dir(d)
+
+
 def make_model_dir(cfg: dict, seed: int, dtype=torch.bfloat16, where: str | None = None) -> str:
     """Writes a random model folder into a temporary place and returns it."""
     from torchless_rs_b200 import write_random_model
     from torchless_rs_b200.config import config_from_dict
-    d = where or tempfile.mkdtemp(prefix="tl_model_")
+    d = where
+    if d is None:
+        d = tempfile.mkdtemp(prefix="tl_model_")
+        _made.append(d)          # removed when the interpreter exits, if not before
     # drawn on the GPU where there is one (the same bits as on the host, much faster)
     device = "cuda:0" if torch.cuda.is_available() and dtype != torch.float16 else "cpu"
     write_random_model(config_from_dict(cfg), d, seed, dtype, device)

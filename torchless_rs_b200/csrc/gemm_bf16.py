@@ -34,6 +34,10 @@ class GemmBf16:
     def __init__(self):
         self.lib = build.load_library("gemm_tc")
         self.lib.tl_gemm_tc.restype = c_int
+        # declared once, so that a call passes plain numbers (no ctypes object per argument)
+        P, I = c_void_p, c_int
+        self.lib.tl_gemm_tc.argtypes = [P, I, P, I, P, I, I, I, I, I, I, P, I, I, c_float, P, P, I, P,
+                                        ctypes.POINTER(c_int), P, ctypes.POINTER(c_int), P]
         self.lib.tl_gemm_tc_take_error.restype = c_int
         register_error_word("gemm_tc", self.take_error)
         self._scratch = {}
@@ -69,16 +73,18 @@ class GemmBf16:
         applied = c_int(0)
         ss_in = scaled.ss if scaled is not None else None
         nw, carry = emit if emit is not None else (None, None)
+        for t in (a, w, out):
+            if not t.is_cuda:
+                raise KernelError("kernel argument is not on a CUDA device; this package has no CPU path")
+        addr = lambda t: t.data_ptr() if t is not None else None
         st = self.lib.tl_gemm_tc(
-            _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
-            c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(sms),
-            _ptr(ss_in), c_int(scaled.tiles if scaled is not None else 0),
-            c_int(scaled.size if scaled is not None else 0),
-            c_float(scaled.eps if scaled is not None else 0.0),
-            _ptr(carry.xw if carry is not None else None), _ptr(nw),
-            c_int(1 if (nw is not None and nw.dtype == torch.float32) else 0),
-            _ptr(carry.ss if carry is not None else None), byref(emitted),
-            byref(rope) if rope is not None else c_void_p(0), byref(applied), _stream())
+            a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K, mode, sms,
+            addr(ss_in), scaled.tiles if scaled is not None else 0, scaled.size if scaled is not None else 0,
+            scaled.eps if scaled is not None else 0.0,
+            addr(carry.xw if carry is not None else None), addr(nw),
+            1 if (nw is not None and nw.dtype == torch.float32) else 0,
+            addr(carry.ss if carry is not None else None), byref(emitted),
+            ctypes.cast(byref(rope), c_void_p) if rope is not None else None, byref(applied), _stream())
         if st == -2:
             return False
         _check(st, "gemm_tc")

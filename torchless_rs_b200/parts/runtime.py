@@ -18,8 +18,14 @@ class Workspace:
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self.generation = 0   # goes up whenever a buffer moves; recorded CUDA graphs are then stale
+        self._views: Dict[tuple, torch.Tensor] = {}
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        # the view of a buffer for a shape is kept: making one costs 4 us, and a layer asks for nine
+        vkey = (name, dtype, tuple(shape))
+        view = self._views.get(vkey)
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -29,7 +35,13 @@ class Workspace:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
             self.generation += 1
-        return buf[:n].view(*shape)
+            for k in [k for k in self._views if k[0] == name and k[1] == dtype]:
+                del self._views[k]          # they show the buffer that was replaced
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = buf[:n].view(*shape)
+        self._views[vkey] = view
+        return view
 
     def bytes_held(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
