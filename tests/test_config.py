@@ -51,6 +51,7 @@ def test_missing_required_key_is_named(key):
 @pytest.mark.parametrize("patch,word", [
     ({"num_key_value_heads": 3}, "multiple"), ({"head_dim": 24}, "head_dim"),
     ({"head_dim": 512}, "head_dim"), ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"tie_word_embeddings": True}, "tie_word_embeddings"),
     ({"hidden_size": "64"}, "integer"), ({"rope_theta": -1}, "rope_theta"),
     ({"vocab_size": 0}, "vocab_size"), ({"eos_token_id": 999}, "vocabulary"),
     ({"layer_types": ["full_attention"]}, "layer_types"),

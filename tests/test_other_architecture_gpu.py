@@ -1,7 +1,7 @@
 """An architecture that exists only in this file: its configuration class, its tensor names
 (`wte`, `wpe`, `h.<i>.ln_1`, `h.<i>.attn.*`, `h.<i>.ln_post`, `h.<i>.ln_2`, `h.<i>.ffn.*`,
-`ln_f`, `out`), a block kind with three norms, an embedding multiplier, a learned position
-table and a soft cap of the logits.  It is registered, written as a model folder, loaded
+`ln_f`; the head is the embedding table), a block kind with three norms, an embedding multiplier, a
+learned position table and a soft cap of the logits.  It is registered, written as a model folder, loaded
 through the package's entry point and stepped, with no change to the package's files, and
 compared with the same arrangement put together from the plain parts.  It is a toy for the
 interfaces; it is nobody's model."""
@@ -89,7 +89,7 @@ def _register():
                           position=PartSpec("rope_half_split", {"head_dim": self.d_head, "theta": self.theta}))
                 for i in range(self.n_layer))
             return ModelSpec(hidden_size=self.n_embd, vocab_size=self.n_vocab, embedding_name="wte.weight",
-                             head_name="out.weight", tie_head_to_embedding=False, final_norm=norm,
+                             head_name="out.weight", tie_head_to_embedding=True, final_norm=norm,
                              final_norm_prefix="ln_f", layers=layers, order=tuple(range(self.n_layer)),
                              embedding_scale=math.sqrt(self.n_embd), position_table_name="wpe.weight",
                              max_positions=self.n_pos, logit_softcap=self.cap)
@@ -112,7 +112,7 @@ def _plain_logits(w, toks):
         h = h + plain.rmsnorm(a, lw["ln_post.weight"], CFG["eps"])
         h = h + plain.swiglu(plain.rmsnorm(h, lw["ln_2.weight"], CFG["eps"]), lw["ffn.gate_proj.weight"],
                              lw["ffn.up_proj.weight"], lw["ffn.down_proj.weight"])
-    logits = plain.rmsnorm(h, w["ln_f.weight"], CFG["eps"]) @ w["out.weight"].T
+    logits = plain.rmsnorm(h, w["ln_f.weight"], CFG["eps"]) @ w["wte.weight"].T      # the head is tied
     return CFG["cap"] * np.tanh(logits / CFG["cap"])
 
 
@@ -126,6 +126,7 @@ def test_an_architecture_defined_outside_the_package(dtype, tmp_path):
     d = tl.write_random_model(cfg, str(tmp_path), 17, store)
     w = read_weights_numpy(d)
     assert "h.1.attn.k_proj.weight" in w and "h.0.ln_post.weight" in w and "wpe.weight" in w
+    assert "out.weight" not in w, "a tied head has no tensor of its own"
     m = tl.load(d, dtype=dtype, max_tokens=512)
     assert type(m.config).__name__ == "ToyConfig"
     rng = np.random.default_rng(5)

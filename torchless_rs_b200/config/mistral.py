@@ -112,6 +112,11 @@ class MistralConfig:
             raise ConfigError(
                 f"{where}: head_dim {self.head_dim} is not supported: the attention kernels take "
                 f"head sizes from 16 to 256 in steps of {HEAD_DIM_STEP}")
+        if self.tie_word_embeddings:
+            # the reference loads lm_head.weight as a tensor of its own (src/model/mod.rs:369) and its
+            # Mistral traits say tie_embeddings = false (src/model/architecture.rs:491)
+            raise ConfigError(f"{where}: tie_word_embeddings is true, but this architecture's head is a "
+                              f"tensor of its own (lm_head.weight)")
         if self.hidden_act != "silu":
             raise ConfigError(f"{where}: hidden_act '{self.hidden_act}' is not supported (only 'silu')")
         for t in self.eos_token_ids:
