@@ -1375,10 +1375,11 @@ static int launch_pair(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs a,
 
 #define MAX_SPLITS 8   // portable cluster size
 
-// How many clusters of `s` blocks of the few-token kernel the GPU is sure to hold at once, two blocks
-// per SM: twice what the occupancy calculation grants at one block per SM (which is what it answers
-// for kernels that take tensor memory).  The GPCs differ in size, so this is not slots / s: this pool's
-// B200 holds 46 clusters of 6 but 39 of 7 and 35 of 8.  -1 if the calculation fails.
+// How many clusters of `s` blocks of the few-token kernel the GPU is sure to hold at once: what the
+// occupancy calculation grants at one block per SM (which is what it answers for kernels that take
+// tensor memory), twice that where two blocks share an SM.  The GPCs differ in size, so this is not
+// slots / s: at two blocks per SM this pool's B200 holds 46 clusters of 6 but 39 of 7 and 35 of 8.
+// -1 if the calculation fails.
 template <int BN, bool SWIGLU>
 static int clusters_at_once_of(int s, size_t smem) {
   cudaLaunchConfig_t cfg = {};
@@ -1396,22 +1397,28 @@ static int clusters_at_once_of(int s, size_t smem) {
                            (int)smem) != cudaSuccess) { cudaGetLastError(); return -1; }
   int n = 0;
   if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, SWIGLU>, &cfg) != cudaSuccess) { cudaGetLastError(); return -1; }
-  return 2 * n;
+  return n;
 }
-static int clusters_at_once(int bn, bool swiglu, int s, size_t smem) {
-  static int known[3][2][MAX_SPLITS + 1];   // token tiles of 16, 32, 64; 0 = not asked yet
+static int clusters_at_once(int bn, bool swiglu, int s, size_t smem, int per_sm) {
+  static int known[5][2][MAX_SPLITS + 1];   // token tiles of 16, 32, 64, 128, 256; 0 = not asked yet
   static std::mutex mu;
-  const int bi = bn == 16 ? 0 : bn == 32 ? 1 : 2;
+  const int bi = bn == 16 ? 0 : bn == 32 ? 1 : bn == 64 ? 2 : bn == 128 ? 3 : 4;
   std::lock_guard<std::mutex> lock(mu);
   int& v = known[bi][swiglu ? 1 : 0][s];
   if (v == 0) {
     int n = -1;
-    if (bn == 16) n = swiglu ? clusters_at_once_of<16, true>(s, smem) : clusters_at_once_of<16, false>(s, smem);
-    else if (bn == 32) n = swiglu ? clusters_at_once_of<32, true>(s, smem) : clusters_at_once_of<32, false>(s, smem);
-    else n = swiglu ? clusters_at_once_of<64, true>(s, smem) : clusters_at_once_of<64, false>(s, smem);
+#define ASK(BN_) n = swiglu ? clusters_at_once_of<BN_, true>(s, smem) : clusters_at_once_of<BN_, false>(s, smem)
+    switch (bn) {
+      case 16: ASK(16); break;
+      case 32: ASK(32); break;
+      case 64: ASK(64); break;
+      case 128: ASK(128); break;
+      default: ASK(256); break;
+    }
+#undef ASK
     v = n <= 0 ? -1 : n;
   }
-  return v;
+  return v < 0 ? v : v * per_sm;
 }
 
 // What the caller passes to have rotation and cache write done by the q/k/v product.
@@ -1471,10 +1478,10 @@ extern "C" int tl_gemm_tc(const void* X, int ldx, const void* W, int ldw, void* 
     // 3, 5, 6 or 7 splits where that puts more blocks on the GPU and all their clusters are sure to run
     // at once (measured at 8 tokens: 5120 x 14336 in 6 splits 26.0 us, in 4 splits 28.9 us, in 7, which
     // do not all fit, 36.6 us; 6144 x 5120 in 5 splits 12.5 us, in 4 splits 13.5 us, in 6 19.5 us)
-    if (two_per_sm && m_tiles == 1) {
+    if (m_tiles == 1) {
       for (int sp = MAX_SPLITS - 1; sp > splits; --sp) {
         if ((sp & (sp - 1)) == 0 || tiles * sp > slots || sp > kb_np / 2) continue;
-        if (tiles <= clusters_at_once(bn, swiglu, sp, budget)) { splits = sp; break; }
+        if (tiles <= clusters_at_once(bn, swiglu, sp, budget, two_per_sm ? 2 : 1)) { splits = sp; break; }
       }
     }
     // token tiles of 128: the reduction of so wide a tile costs about as much as 16 K-blocks of 64
