@@ -184,6 +184,10 @@ class Engine:
         a prompt's end up to a quarter more) until its prompt runs out; the result does not depend
         on the cut beyond rounding."""
         B = len(slots)
+        if len(prompts) != B:
+            raise ValueError("one prompt per slot is needed")
+        if any(len(p) == 0 for p in prompts):
+            raise ValueError("every sequence of a step brings at least one token")
         budget = tokens_per_step or self.PREFILL_TOKENS_PER_STEP
         total = sum(len(p) for p in prompts)
         if total <= budget:
