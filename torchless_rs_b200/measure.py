@@ -159,13 +159,22 @@ MISTRAL_7B_SIZES = {
     "max_position_embeddings": 32768, "hidden_act": "silu", "tie_word_embeddings": False,
     "torch_dtype": "bfloat16",
 }
+# the layer sizes of the two larger workloads that bench.py names (Mistral NeMo 12B, Mistral Small 22B)
+MODEL_SIZES = {
+    "mistral7b": MISTRAL_7B_SIZES,
+    "nemo12b": dict(MISTRAL_7B_SIZES, hidden_size=5120, vocab_size=131072, rope_theta=1e6, sliding_window=None,
+                    max_position_embeddings=131072),
+    "small22b": dict(MISTRAL_7B_SIZES, hidden_size=6144, num_attention_heads=48, intermediate_size=16384,
+                     vocab_size=32768, rope_theta=1e6, sliding_window=None),
+}
+SIZES = MISTRAL_7B_SIZES   # what `step` and `timeline` build; --model chooses
 
 
 def step(B: int, context: int, prefill: int, layers: int, iters: int) -> None:
     from . import from_random
     from .config import config_from_dict
     from .sampling.params import SamplingParams
-    cfg = dict(MISTRAL_7B_SIZES, num_hidden_layers=layers)
+    cfg = dict(SIZES, num_hidden_layers=layers)
     longest = max(context + iters + 1, prefill)
     model = from_random(config_from_dict(cfg), seed=0, dtype="bfloat16",
                         max_tokens=B * (longest + 64) + prefill + 64, max_batch=B + 1, max_seq_len=longest + 64)
@@ -215,7 +224,7 @@ def timeline(B: int, context: int, layers: int) -> None:
     from . import from_random
     from .config import config_from_dict
     from .sampling.params import SamplingParams
-    cfg = dict(MISTRAL_7B_SIZES, num_hidden_layers=layers)
+    cfg = dict(SIZES, num_hidden_layers=layers)
     model = from_random(config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=B * (context + 128),
                         max_batch=B, max_seq_len=context + 128)
     eng = model.engine
@@ -280,9 +289,13 @@ def main() -> None:
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
+    ap.add_argument("--model", default="mistral7b", choices=sorted(MODEL_SIZES),
+                    help="step, timeline: whose layer sizes the model has")
     ap.add_argument("--splits", type=int, default=0,
                     help="attn-decode, timeline: this many key splits instead of the engine's choice")
     a = ap.parse_args()
+    global SIZES
+    SIZES = MODEL_SIZES[a.model]
     if a.splits:
         from .csrc import attention_bf16
         attention_bf16.decode_splits = lambda *args, **kw: a.splits
