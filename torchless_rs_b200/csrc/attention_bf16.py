@@ -27,14 +27,43 @@ for _hd in FAST_HEAD_DIMS:
                            (f"-DHEAD_DIM={_hd}",))
 
 
-def decode_splits(batch_size: int, nkv: int, max_len: int, window, target_blocks: int = TARGET_BLOCKS) -> int:
-    """How many blocks share the keys of one (sequence, kv head): enough for one wave of
-    `target_blocks` blocks, never more than there is work."""
+# What the split rule knows about the decode kernel (measured on a B200, head size 128, `measure attn-decode`):
+BLOCK_GBS = 33.0      # one block alone streams its pages at about this rate (three pages in flight)
+HBM_GBS = 6500.0      # all blocks together
+MERGE_US = 2.5        # the merge kernel that more than one split needs
+SPLIT_US = 0.03       # and what every further split adds to it
+WAVE_US = 1.0         # set-up and the write of the partial results, once per wave of blocks
+
+
+def decode_splits(batch_size: int, nkv: int, max_len: int, window, target_blocks: int = TARGET_BLOCKS,
+                  head_dim: int = 128) -> int:
+    """How many blocks share the keys of one (sequence, kv head): the count with the least estimated
+    time, never more than there is work.  The estimate: blocks run in waves of `target_blocks`; a block
+    takes its pages at BLOCK_GBS unless the wave together exceeds HBM_GBS; several splits cost a merge.
+    It gives one full wave where the (sequence, kv head) pairs are few (8 sequences of 4096 tokens and 8
+    kv heads: 4 splits, 24.8 us; 1 sequence: 32 splits), and where they are more than one wave it cuts
+    them finer so that the last wave is not a nearly empty one (40 sequences: 4 splits 111 us, 1 split
+    138 us; 20 sequences: 3 splits 57 us, 1 split 63 us; 24 or 32 sequences: 1 split)."""
     span = min(max_len, window) if window else max_len
     groups = (span + 31) // 32 + 1
     by_work = max(1, (groups + 3) // 4)          # at least one 32-key group per warp
-    by_fill = max(1, target_blocks // max(1, batch_size * nkv))
-    return max(1, min(by_work, by_fill, 32))   # 32: the merge kernel fetches that many splits in one round of loads
+    cap = min(by_work, 32)                       # 32: the merge kernel fetches that many splits in one round of loads
+    units = max(1, batch_size * nkv)
+    one_wave = max(1, min(cap, target_blocks // units))   # as many splits as fill one wave
+    pages = (span + build.PAGE_TOKENS - 1) // build.PAGE_TOKENS
+    page_us = build.PAGE_TOKENS * head_dim * 4 / (BLOCK_GBS * 1e3)     # keys and values, two bytes each
+    together = HBM_GBS / BLOCK_GBS               # blocks that saturate the memory
+    best, best_t = 1, None
+    # the one-wave count against 1 to 4 splits (what was measured where the pairs exceed a wave)
+    for s in sorted(set([one_wave] + [c for c in (1, 2, 3, 4) if c <= cap])):
+        full, rest = divmod(units * s, target_blocks)
+        waves = full * max(target_blocks / together, 1.0) + (max(rest / together, 1.0) if rest else 0.0)
+        t = -(-pages // s) * page_us * waves + WAVE_US * (full + (1 if rest else 0))
+        if s > 1:
+            t += MERGE_US + SPLIT_US * s
+        if best_t is None or t < 0.98 * best_t:      # more splits only for a gain the estimate can resolve
+            best, best_t = s, t
+    return best
 
 
 class AttentionBf16:
@@ -154,7 +183,8 @@ class AttentionBf16:
         if self.lib is None or nh // nkv > MAX_GROUP:
             return False
         if batch.is_decode:
-            n_splits = decode_splits(batch.n_seqs, nkv, batch.len_bucket, window, self._target_blocks(q.device))
+            n_splits = decode_splits(batch.n_seqs, nkv, batch.len_bucket, window, self._target_blocks(q.device),
+                                     self.head_dim)
             self.decode(q, cache_view.k_pages, cache_view.v_pages, out, batch.seq_len,
                         batch.seq_slot, cache_view.page_table, nh, nkv, window, scale, n_splits,
                         workspace)
