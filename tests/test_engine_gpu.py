@@ -300,6 +300,40 @@ def test_rows_that_end_are_dropped_on_the_device(tiny):
                      f"sequence {i}")
 
 
+def test_one_long_sequence_beside_short_ones(tiny, monkeypatch):
+    """Decoding a sequence of 500 tokens together with five of a few tokens, twice: as the engine plans
+    it, and with the decode attention told to give a block two pages whatever the sequence (what it
+    does by itself where that pays: the long sequence then has four blocks that work, and the short
+    ones' surplus blocks write empty partial results).  Every sequence's logits are the plain
+    implementation's both times, through the recorded graph too."""
+    from torchless_rs_b200.csrc import attention_bf16
+    lens = [500, 3, 70, 1, 100, 20]
+    reqs = _requests(tiny, [n + 6 for n in lens], 71)
+    for forced in (False, True):
+        if forced:
+            splits_of = attention_bf16.decode_splits
+            # (the kernel for head size 32 has no page quantum: it is asked without the lengths)
+            monkeypatch.setattr(attention_bf16, "decode_plan",
+                                lambda *a: (6, 2) if len(a) > 6 and a[6] is not None else (splits_of(*a[:6]), 0))
+            tiny.engine._graphs.clear()
+            tiny.engine._seen.clear()
+        slots = tiny.engine.start_sequences(len(lens))
+        got = [[] for _ in lens]
+        tiny.step_np(slots, [r[:n] for r, n in zip(reqs, lens)], "last")
+        for step in range(6):
+            out = tiny.step_np(slots, [[r[n + step]] for r, n in zip(reqs, lens)], "last")
+            for i in range(len(lens)):
+                got[i].append(out[i:i + 1])
+        tiny.engine.cache.check()
+        tiny.engine.end_sequences(slots)
+        for i, (r, n) in enumerate(zip(reqs, lens)):
+            assert_close(np.concatenate(got[i]), tiny.reference(r)[n:n + 6], tiny.dtype,
+                         f"sequence {i} of {n} tokens, {'two pages a block' if forced else 'as planned'}")
+    monkeypatch.undo()
+    tiny.engine._graphs.clear()
+    tiny.engine._seen.clear()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [None, 1500])
 def test_long_context(dtype, window):

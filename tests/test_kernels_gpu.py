@@ -251,6 +251,18 @@ def test_attention_decode_bf16(nh, nkv, hd, window, use_tma):
         for b in range(B):
             assert torch.allclose(got[b], refs[b], **_attn_tol(dtype)), \
                 f"splits {n_splits} seq {b} (len {lens[b]})"
+    if use_tma and hd % 64 == 0:
+        # a block takes `quantum` pages whatever the sequence's length: long sequences use many of the
+        # splits, short ones few (their other blocks write empty partial results); with too few
+        # splits for the longest sequence the last block takes the rest
+        for quantum, n_splits in ((1, 16), (2, 8), (5, 4), (3, 3), (16, 1), (7, 32)):
+            out = torch.full((B, nh * hd), float("nan"), dtype=dtype, device=DEV)
+            att.decode(q, pc.k_pages, pc.v_pages, out, seq_len, pc.seq_slot, pc.table, nh, nkv, window,
+                       scale, n_splits, ws, quantum=quantum)
+            got = out.cpu().double().view(B, nh, hd)
+            for b in range(B):
+                assert torch.allclose(got[b], refs[b], **_attn_tol(dtype)), \
+                    f"quantum {quantum} splits {n_splits} seq {b} (len {lens[b]})"
     # the same bits every time
     first = None
     for _ in range(12):

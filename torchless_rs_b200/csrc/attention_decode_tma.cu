@@ -78,7 +78,7 @@ FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __gri
                            __nv_bfloat16* __restrict__ out,
                            const int* __restrict__ seq_len, const int* __restrict__ seq_slot,
                            const int* __restrict__ page_table, int table_stride, int nh, int nkv,
-                           int window, float scale_log2, int n_splits) {
+                           int window, float scale_log2, int n_splits, int quantum) {
   TL_TRACE_SCOPE(4, n_splits, 4);
   extern __shared__ uint8_t td_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)td_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -109,9 +109,26 @@ FN(attn_decode_tma_kernel)(const __grid_constant__ CUtensorMap tm_k, const __gri
   const int lo = (window > 0 && len - window > 0) ? len - window : 0;
   const int* table = page_table + (size_t)seq_slot[b] * table_stride;
   const int first_page = lo / PAGE, last_page = (len - 1) / PAGE;
-  const int per = (last_page - first_page + 1 + n_splits - 1) / n_splits;
+  // quantum 0: every sequence is cut into n_splits equal shares.  quantum > 0: a block takes that many
+  // pages whatever the sequence's length (sequences of unequal lengths: the long ones get more blocks
+  // that work, the short ones' later blocks find nothing and write an empty partial result); the
+  // last block takes what is left, should the host have counted short.
+  const int per = quantum > 0 ? quantum : (last_page - first_page + 1 + n_splits - 1) / n_splits;
   const int ps = first_page + split * per;
-  const int n_pg = max(0, min(ps + per, last_page + 1) - ps);
+  const int n_pg = max(0, (split == n_splits - 1 ? last_page + 1 : min(ps + per, last_page + 1)) - ps);
+
+  if (n_pg == 0 && n_splits > 1) {
+    // nothing of this sequence lies in this block's share (a short sequence beside long ones): an
+    // empty partial result, marked by a sum of zero, and no more
+    pdl_wait();   // the merge kernel of the step before may still read the partial results
+    pdl_launch_dependents();
+    if (threadIdx.x < G) {
+      float* dst = part + (((size_t)b * nh + kvh * G + threadIdx.x) * n_splits + split) * PART_STRIDE;
+      dst[HEAD_DIM] = -INFINITY;
+      dst[HEAD_DIM + 1] = 0.0f;
+    }
+    return;
+  }
 
   // one thread requests pages; `issue(i)` brings page ps + i into stage i % TD_STAGES
   auto issue = [&](int i) -> bool {
@@ -496,9 +513,10 @@ FN(attn_decode_tma_combine_kernel)(const float* __restrict__ part, __nv_bfloat16
     for (int w = 1; w < HEAD_DIM / 32; ++w) l += red_s[HEAD_DIM / 32 + w];
     float acc = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < n_splits) acc += f_s[j] * v[j];
-    for (int s = 32; s < n_splits; ++s) acc += f_s[s] * src[s * PART_STRIDE + d];
+    for (int j = 0; j < 32; ++j)   // an empty split's values were never written: its factor is 0, its values are not touched
+      if (j < n_splits && f_s[j] != 0.0f) acc += f_s[j] * v[j];
+    for (int s = 32; s < n_splits; ++s)
+      if (f_s[s] != 0.0f) acc += f_s[s] * src[s * PART_STRIDE + d];
     out[((size_t)b * nh + h) * HEAD_DIM + d] = __float2bfloat16_rn(acc / l);
     return;
   }
@@ -508,7 +526,7 @@ FN(attn_decode_tma_combine_kernel)(const float* __restrict__ part, __nv_bfloat16
   for (int s = 0; s < n_splits; ++s) {
     const float sm = src[s * PART_STRIDE + HEAD_DIM];
     const float f = sm == -INFINITY ? 0.0f : exp2f(sm - m);
-    acc += f * src[s * PART_STRIDE + d];
+    if (f != 0.0f) acc += f * src[s * PART_STRIDE + d];
     l += f * src[s * PART_STRIDE + HEAD_DIM + 1];
   }
   out[((size_t)b * nh + h) * HEAD_DIM + d] = __float2bfloat16_rn(acc / l);
@@ -561,17 +579,19 @@ static bool td_make_map(CUtensorMap* map, const void* ptr, long long rows, long 
   return true;
 }
 
-// As tl_attn_decode_hd<N>, plus the number of pages of the storage (for the tensor maps).
+// As tl_attn_decode_hd<N>, plus the number of pages of the storage (for the tensor maps) and `quantum`:
+// 0, or the pages a block takes (see the kernel).
 // Returns -2 for sizes this kernel does not take.
 extern "C" int FN(tl_attn_decode_tma)(const void* q, const void* k_pages, const void* v_pages,
                                       long long n_pages, void* out, float* part, const int* seq_len,
                                       const int* seq_slot, const int* page_table, int table_stride,
                                       int B, int nh, int nkv, int window, float scale, int n_splits,
-                                      cudaStream_t stream) {
+                                      int quantum, cudaStream_t stream) {
 #if HEAD_DIM % 64 != 0
   return -2;
 #else
   if (B <= 0) return 0;
+  if (quantum < 0) return -1;
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || n_splits > 65535 ||
       nkv > 65535 || B > 65535 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
     return -2;
@@ -595,11 +615,11 @@ extern "C" int FN(tl_attn_decode_tma)(const void* q, const void* k_pages, const 
   if (nh / nkv > 8)
     st = tl_launch(FN(attn_decode_tma_kernel)<true>, grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
                    (const __nv_bfloat16*)q, part, (__nv_bfloat16*)out, seq_len, seq_slot, page_table,
-                   table_stride, nh, nkv, window, scale_log2, n_splits);
+                   table_stride, nh, nkv, window, scale_log2, n_splits, quantum);
   else
     st = tl_launch(FN(attn_decode_tma_kernel)<false>, grid, dim3(TD_WARPS * 32), smem, stream, tk, tv,
                    (const __nv_bfloat16*)q, part, (__nv_bfloat16*)out, seq_len, seq_slot, page_table,
-                   table_stride, nh, nkv, window, scale_log2, n_splits);
+                   table_stride, nh, nkv, window, scale_log2, n_splits, quantum);
   if (st || n_splits == 1) return st;   // a single split has written the result itself
   return tl_launch(FN(attn_decode_tma_combine_kernel), dim3(nh, B), dim3(HEAD_DIM), 0, stream,
                    (const float*)part, (__nv_bfloat16*)out, nh, n_splits);

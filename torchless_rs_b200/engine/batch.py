@@ -36,6 +36,25 @@ class StepBatch:
     past_lens: List[int]
     new_lens: List[int]
     token_src: Optional[torch.Tensor] = None   # device int32: tokens selected by the previous step
+    total_bucket: Optional[int] = None           # the sum of the sequences' lengths after this step, rounded up
+
+
+def length_bucket(max_len: int) -> int:
+    """The longest sequence's length rounded up to a power of two (at least 256)."""
+    return max(256, 1 << max(max_len - 1, 0).bit_length())
+
+
+def total_bucket(lens: Sequence[int]) -> int:
+    """The sum of the lengths rounded up to the next of 1, 1.25, 1.5, 1.75 times a power of two (at least
+    256): what a recorded decode step may assume about how the keys are spread over the sequences."""
+    total = int(sum(lens))
+    if total <= 256:
+        return 256
+    base = 1 << ((total - 1).bit_length() - 1)       # base < total <= 2 base
+    for q in (5, 6, 7, 8):
+        if total <= base * q // 4:
+            return base * q // 4
+    return 2 * base
 
 
 def layout_step(past_lens: Sequence[int], counts: Sequence[int], slots: Sequence[int],
@@ -118,7 +137,7 @@ class BatchStager:
         max_len = max(new_lens)
         return StepBatch(
             n_tokens=n, n_seqs=n, n_want=n, is_decode=True, max_new=1, max_len=max_len,
-            len_bucket=max(256, 1 << max(max_len - 1, 0).bit_length()),
+            len_bucket=length_bucket(max_len), total_bucket=total_bucket(new_lens),
             slots=list(slots), past_lens=list(past_lens), new_lens=list(new_lens), **views)
 
     def stage(self, arrays: dict, slots, past_lens, is_decode: bool) -> StepBatch:
@@ -144,6 +163,7 @@ class BatchStager:
         return StepBatch(
             n_tokens=sizes[0], n_seqs=sizes[3], n_want=sizes[6], is_decode=is_decode,
             max_new=int(counts.max()) if len(counts) else 0,
-            max_len=max_len, len_bucket=max(256, 1 << max(max_len - 1, 0).bit_length()),
+            max_len=max_len, len_bucket=length_bucket(max_len),
+            total_bucket=total_bucket([int(x) for x in arrays["seq_len"]]),
             slots=list(slots), past_lens=list(past_lens),
             new_lens=[int(x) for x in arrays["seq_len"]], **views)

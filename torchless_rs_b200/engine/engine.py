@@ -16,7 +16,7 @@ from ..cache import Cache
 from ..config.spec import ModelSpec
 from ..csrc import ops
 from ..parts.runtime import Runtime
-from .batch import BatchStager, StepBatch, layout_step
+from .batch import BatchStager, StepBatch, layout_step, length_bucket, total_bucket
 from .model import DecoderModel
 
 
@@ -130,7 +130,8 @@ class Engine:
                 self.rt.ops.advance_step(batch.token_pos, batch.seq_len)
                 batch.past_lens, batch.new_lens = list(past), list(new_lens)
                 batch.max_len = max(new_lens)
-                batch.len_bucket = max(256, 1 << max(batch.max_len - 1, 0).bit_length())
+                batch.len_bucket = length_bucket(batch.max_len)
+                batch.total_bucket = total_bucket(new_lens)
                 batch.token_src = token_src
                 self.steps_advanced_on_device += 1
                 logits = self._forward(batch)
@@ -217,7 +218,7 @@ class Engine:
         second step of a shape is recorded as a CUDA graph and later ones replay it."""
         if not (self.use_graphs and batch.is_decode and self.model.graph_safe):
             return self.model.forward(batch)
-        key = (batch.n_seqs, batch.n_want, batch.len_bucket, self.rt.workspace.generation,
+        key = (batch.n_seqs, batch.n_want, batch.len_bucket, batch.total_bucket, self.rt.workspace.generation,
                batch.tokens.data_ptr(), batch.token_src.data_ptr() if batch.token_src is not None else 0)
         hit = self._graphs.get(key)
         if hit is not None:
@@ -236,7 +237,7 @@ class Engine:
             logits = self.model.forward(batch)
         recorded = ops.counts_since(before)   # recording launches nothing; replay runs them all
         ops.add_launches(recorded, -1)
-        if self.rt.workspace.generation != key[3]:   # a buffer moved while recording
+        if self.rt.workspace.generation != key[4]:   # a buffer moved while recording
             return self.model.forward(batch)
         self._graphs[key] = (graph, logits, batch, recorded)
         graph.replay()
