@@ -181,9 +181,9 @@ class Engine:
         """Feeds the prompts of sequences that start together and returns the 32-bit logits
         [sequences, vocab] at each prompt's last token (a buffer of its own, valid until the next
         call).  Prompts whose tokens together exceed `tokens_per_step` are fed in several steps, every
-        sequence going on by the same number of tokens (a multiple of the page size, at least 128;
-        a prompt's end up to a quarter more) until its prompt runs out; the result does not depend
-        on the cut beyond rounding."""
+        sequence that still has tokens going on by the same number of them (a multiple of the page
+        size, at least 128; a prompt's end up to a quarter more); the result does not depend on the
+        cut beyond rounding."""
         B = len(slots)
         if len(prompts) != B:
             raise ValueError("one prompt per slot is needed")
@@ -193,13 +193,15 @@ class Engine:
         total = sum(len(p) for p in prompts)
         if total <= budget:
             return self.step(slots, [list(p) for p in prompts], "last")
-        chunk = max(128, budget // B // 64 * 64)
         out = self.rt.workspace.get("prefill_logits", (B, self.vocab_size), torch.float32)
         fed = [0] * B
         while True:
             rows = [b for b in range(B) if fed[b] < len(prompts[b])]
             if not rows:
                 return out
+            # the sequences that still have tokens share the step: when the short prompts have run
+            # out, the long ones go on in larger pieces
+            chunk = max(128, budget // len(rows) // 64 * 64)
             # a prompt's last tokens do not get a step of their own: up to a quarter more goes now
             toks = [list(prompts[b][fed[b]:fed[b] + (chunk if len(prompts[b]) - fed[b] > chunk + chunk // 4
                                                        else len(prompts[b]))]) for b in rows]
