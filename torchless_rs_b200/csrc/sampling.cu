@@ -191,10 +191,12 @@ __device__ __forceinline__ u64 blk_scan(u64 v, SampleShared& sm, u64* total) {
 // queue a thousand threads on two or three bins).  Every lane of the warp must call these;
 // `bin` < 0 takes no part.
 __device__ __forceinline__ void warp_count(uint32_t* cnt, int bin) {
+  if (!__any_sync(0xffffffffu, bin >= 0)) return;   // after the first digits few entries still carry the prefix
   const unsigned peers = __match_any_sync(0xffffffffu, bin);
   if (bin >= 0 && (int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[bin], (uint32_t)__popc(peers));
 }
 __device__ __forceinline__ void warp_count_weight(uint32_t* cnt, u64* wsum, int bin, u64 w) {
+  if (!__any_sync(0xffffffffu, bin >= 0)) return;   // (as above: most warps have nothing to add in the later passes)
   const unsigned peers = __match_any_sync(0xffffffffu, bin);
   // the weights have 41 bits: three sums of 16-bit (and 9-bit) pieces cannot overflow 32 bits
   const uint32_t a = __reduce_add_sync(peers, (uint32_t)(w & 0xffffull));
