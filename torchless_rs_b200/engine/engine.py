@@ -168,13 +168,15 @@ class Engine:
         self.cache.commit(slots, new_lens)
         return logits
 
-    # Tokens per step beyond which a batch of prompts is fed in several steps.  Measured on 8 layers in
-    # bfloat16: 8 prompts of 8192 tokens at the layer sizes of Mistral NeMo 12B take 324 to 338 ms in one
-    # step, 316 ms in steps of 16,384 tokens, 297 ms at 8192, 286 ms at 4096 and 304 ms at 2048; 16
-    # prompts of 128 to 4096 tokens at the sizes of Mistral Small 22B 245 / 249 / 224 / 221 / 243 ms.
-    # While a step's activations stay near the size of the L2 cache, the kernels between the products
-    # find them there; below that the products' tiles no longer fill the GPU.
-    PREFILL_TOKENS_PER_STEP = 4096
+    # Tokens per step beyond which a batch of prompts is fed in several steps: a bound on the workspace (a
+    # step of 65,536 tokens at the layer sizes of Mistral NeMo 12B holds some 6 GB of activations), not a
+    # gain in time.  Measured on 8 layers in bfloat16 since the many-token products walk their tiles in
+    # groups of weight strips: 8 prompts of 8192 tokens at the NeMo sizes 274 to 277 ms in one step, 274 ms in
+    # steps of 16,384 tokens, 277 at 8192, 284 at 4096; 16 prompts of 128 to 4096 tokens at the sizes of Mistral
+    # Small 22B 202 to 208 / 201 to 210 / 209 to 216 / 218 ms; one prompt of 16,384 tokens at the 7B sizes 52 /
+    # 51 / 56 / 60 ms.  (Before that change one step of 65,536 tokens took 337 ms and steps of 4096 tokens 286:
+    # the large step's products read their activations again for every strip of weights.)
+    PREFILL_TOKENS_PER_STEP = 65536
 
     def prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]],
                 tokens_per_step: Optional[int] = None) -> torch.Tensor:
