@@ -320,7 +320,9 @@ def test_attention_decode_far_key_stands_out(use_tma):
                                    (300, 4096, 1024), (130, 6100, 768), (70, 4096, 4096),
                                    (300, 256, 14336), (200, 384, 8192), (513, 384, 256), (140, 256, 512),
                                    # K in 6, 5 and 3 splits (40, 48 and 80 tiles of 128 rows), and 129 to 256 tokens on single SMs
-                                   (8, 5120, 4096), (3, 6144, 1280), (40, 6100, 1000), (12, 10240, 1024), (200, 4096, 4096)])
+                                   (8, 5120, 4096), (3, 6144, 1280), (40, 6100, 1000), (12, 10240, 1024), (200, 4096, 4096),
+                                   # 24 token tiles and more: weight strips in groups of 8 (3 strips; 8 + 1; 8 + 8 + 4 with a ragged edge)
+                                   (6200, 520, 328), (8192, 2304, 256), (6150, 5000, 136)])
 def test_gemm_tensor_core(M, N, K):
     from torchless_rs_b200.csrc.gemm_bf16 import GemmBf16
     g = GemmBf16.get()
