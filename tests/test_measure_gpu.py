@@ -14,6 +14,7 @@ pytestmark = pytest.mark.gpu
     ["attn-decode", "2", "300", "--iters", "3"],
     ["attn-prefill", "256", "--iters", "2"],
     ["elementwise", "64"],
+    ["decode", "700", "90", "90", "--layers", "1"],
 ])
 def test_measure_command_runs(args):
     p = subprocess.run([sys.executable, "-m", "torchless_rs_b200.measure", *args], capture_output=True, text=True,

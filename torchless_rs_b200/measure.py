@@ -211,6 +211,52 @@ def step(B: int, context: int, prefill: int, layers: int, iters: int) -> None:
     eng.check_kernels()
 
 
+def decode(lengths, layers: int, window, equal_shares: bool) -> None:
+    """Decode steps as generation runs them (replayed CUDA graph, tokens fed from the device's own choice)
+    for sequences that end at the given lengths: us per step and the share of the copy bandwidth that the
+    bytes a step has to read would need.  `equal_shares`: the decode attention without its page quantum."""
+    from . import from_random
+    from .config import config_from_dict
+    from .csrc import attention_bf16
+    from .sampling.params import SamplingParams
+    cfg = dict(SIZES, num_hidden_layers=layers, sliding_window=window, max_position_embeddings=1 << 20)
+    B, steps, warm = len(lengths), 32, 6
+    model = from_random(config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=sum(n + 128 for n in lengths),
+                        max_batch=B, max_seq_len=max(lengths) + 128)
+    eng = model.engine
+    for g in eng.cache.paged:
+        g.storage.normal_(0.0, 0.5)
+    if equal_shares:
+        plain = attention_bf16.decode_splits
+        attention_bf16.decode_plan = lambda *a, **k: (plain(*a[:6]), 0)
+    slots = eng.start_sequences(B)
+    start = [max(1, n - steps - warm) for n in lengths]
+    eng.cache.prepare(slots, start)
+    eng.cache.commit(slots, start)
+    toks = [[(7 * i + 3) % eng.vocab_size] for i in range(B)]
+    greedy = SamplingParams.greedy()
+    for _ in range(warm):
+        model.sampler.select(eng.step(slots, toks, "last"), greedy)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        model.sampler.select(eng.step(slots, toks, "last"), greedy)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / steps
+    c = config_from_dict(cfg)
+    per_layer = 2 * c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim \
+        + 2 * c.hidden_size * c.num_attention_heads * c.head_dim + 2 * 3 * c.hidden_size * c.intermediate_size
+    spans = [min(n, window) if window else n for n in lengths]
+    byts = layers * per_layer + 2 * c.hidden_size * c.vocab_size \
+        + layers * sum(spans) * c.num_key_value_heads * c.head_dim * 4
+    eng.end_sequences(slots)
+    eng.check_kernels()
+    print(f"decode, {B} sequences of {min(lengths)} to {max(lengths)} tokens ({sum(lengths)} in all), {layers} layers + head"
+          f"{', equal shares' if equal_shares else ''}: {us:.1f} us per step, {byts / us / 1e3:.0f} GB/s of weights and cache")
+
+
 TRACE_KINDS = {1: "embed", 2: "rmsnorm", 3: "product", 4: "attention", 5: "attention merge", 6: "argmax"}
 
 
@@ -285,12 +331,15 @@ def timeline(B: int, context: int, layers: int) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "step", "timeline"])
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "step", "timeline", "decode"])
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
     ap.add_argument("--model", default="mistral7b", choices=sorted(MODEL_SIZES),
                     help="step, timeline: whose layer sizes the model has")
+    ap.add_argument("--window", type=int, default=0, help="decode: the sliding window (0: none)")
+    ap.add_argument("--equal-shares", action="store_true",
+                    help="decode: every sequence's keys in equal shares (no page quantum)")
     ap.add_argument("--splits", type=int, default=0,
                     help="attn-decode, timeline: this many key splits instead of the engine's choice")
     a = ap.parse_args()
@@ -307,6 +356,8 @@ def main() -> None:
         timeline(a.sizes[0], a.sizes[1], a.layers)
     elif a.what == "step":
         step(a.sizes[0], a.sizes[1], a.sizes[2], a.layers, min(a.iters, 8))
+    elif a.what == "decode":
+        decode(a.sizes, a.layers, a.window or None, a.equal_shares)
     elif a.what == "attn-decode":
         attn_decode(a.sizes[0], a.sizes[1], a.iters)
     else:
